@@ -78,7 +78,8 @@ class CacheManager:
         self._needs: List[Optional[Tuple]] = []
         self._entry_group: Dict[Tuple[int, int], Tuple[int, int]] = {}
         self._state: Dict[Tuple[int, int], torch.Tensor] = {}
-        self._cache_from = list(cache_from)
+        # requirements beyond the schedule's entries belong to the model itself (its embedder's state): nobody shares them
+        self._cache_from = list(cache_from) + [None] * (len(requirements) - len(cache_from))
         for e, need in enumerate(requirements):
             if need is None:
                 self._needs.append(None)
@@ -104,7 +105,13 @@ class CacheManager:
         # the writes of padding rows (a decode batch padded up to a captured width).
         for g in self.groups:
             n = g.need
-            if n.v_head_dim is None or n.v_head_dim == n.head_dim:
+            if n.v_head_dim == 0:
+                # no value rows: the mixer reads its values out of the key rows
+                g.tensor = torch.zeros((len(g.entries), 1, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
+                                       dtype=dtype, device=device)
+                g.k = [g.tensor[i, 0] for i in range(len(g.entries))]
+                g.v = [None] * len(g.entries)
+            elif n.v_head_dim is None or n.v_head_dim == n.head_dim:
                 g.tensor = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
                                        dtype=dtype, device=device)
                 g.k = [g.tensor[i, 0] for i in range(len(g.entries))]
@@ -183,7 +190,7 @@ class CacheManager:
 
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + (g.need.v_head_dim or g.need.head_dim)) * item
+        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * item
                    for g in self.groups)
 
     # ------------------------------------------------------------------ requests

@@ -39,6 +39,9 @@ class LayerSpec:
     # Slot name -> the component of the checkpoint's tensor names that the slot's part goes by, for an
     # arrangement whose checkpoints do not all use the same names (None: the arrangement's own).
     names: Optional[Mapping[str, str]] = None
+    # Constants of the arrangement itself (its constructor's keyword arguments), e.g. the factor of the stream in a
+    # block that normalises after the sum.
+    arrangement_params: Mapping[str, Any] = field(default_factory=dict)
 
 
 def prenorm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
@@ -98,6 +101,9 @@ class ModelSpec:
     bare_tensor_names: bool = False
     # Tensors of the model itself (not of a part): full name -> (shape, role, init) as for a TensorSpec.
     extra_tensors: Mapping[str, Tuple] = field(default_factory=dict)
+    # The part that makes the stream from the step's token ids when a table row is not all of it (None: row
+    # ``embedding_name`` of the table times ``embedding_scale``).  It names its tensors in full and owns the table.
+    embedder: Optional[PartSpec] = None
 
     def validate(self) -> None:
         if not self.layers:

@@ -32,7 +32,14 @@ constexpr int DK = CO_MAPS_DK, DV = CO_MAPS_DV, MAPS = CO_MAPS_N;
 static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 256 && DV <= 256, "head sizes: multiples of 16 up to 256");
 static_assert(MAPS == 1 || MAPS == 2, "one score map or two");
 constexpr int KROW = MAPS * DK;                  // channels of a key row (and of a query head)
-constexpr int KS = KROW + 8, VS = DV + 8;        // padded row strides in shared memory: an odd number of 16-byte units
+#ifdef CO_MAPS_V_IN_K
+constexpr bool V_IN_K = true;                    // the values are the first DV channels of the key row: nothing else is fetched
+static_assert(DV <= KROW, "values inside the key row cannot be wider than it");
+#else
+constexpr bool V_IN_K = false;
+#endif
+constexpr int KS = KROW + 8;                     // padded row strides in shared memory: an odd number of 16-byte units
+constexpr int VS = V_IN_K ? KS : DV + 8;
 constexpr int BM = 64, WARPS = 4;
 #ifdef CO_MAPS_BN
 constexpr int BN = CO_MAPS_BN;                   // a measuring switch: keys per tile
@@ -52,7 +59,12 @@ struct MapsArgs {
   int nh, nkv, page_size, window, chunk, sink, head_norm, skip_single;
   int table_cache;      // block-table entries a CTA of the prompt kernel may keep in shared memory
   float scale_log2, lambda, eps, out_scale;
+  const float* sink_scores;     // [heads]: the sink's score per head (null: 0)
 };
+// the sink's score of head h in the log2 domain
+__device__ __forceinline__ float sink_log2(const MapsArgs& A, int h) {
+  return A.sink_scores ? A.sink_scores[h] * 1.4426950408889634f : 0.f;
+}
 
 __device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(p);
@@ -120,7 +132,7 @@ __device__ __forceinline__ void load_keys(bf16* ks, bf16* vs, const MapsArgs& A,
     bf16* kdst = ks + row * KS;
 #pragma unroll
     for (int ch = sub; ch < KC; ch += TPR) cp_async16(kdst + ch * 8, ksrc + ch * 8, bytes);
-    if (vs) {
+    if (!V_IN_K && vs) {
       const bf16* vsrc = A.v_cache + at * DV;
       bf16* vdst = vs + row * VS;
 #pragma unroll
@@ -287,9 +299,10 @@ __global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kerne
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
       float l = quad_sum(sum[m][rr]), M = mx[m][rr];
-      if (A.sink && M != -INFINITY) {               // one more term exp(0) that carries no value
-        const float M2 = fmaxf(M, 0.f);
-        l = l * ex2(M - M2) + ex2(-M2);
+      if (A.sink && M != -INFINITY) {               // one more term exp(sink score) that carries no value
+        const float sv = sink_log2(A, h);
+        const float M2 = fmaxf(M, sv);
+        l = l * ex2(M - M2) + ex2(sv - M2);
         M = M2;
       }
       if (M == -INFINITY) { M = 0.f; inv[m][rr] = 0.f; }      // a row beyond the portion
@@ -334,7 +347,7 @@ __global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kerne
           for (int e = 0; e < 4; ++e) w[nt][e] -= A.lambda * (ex2(s[nt][e] - mx[MAPS - 1][e >> 1]) * inv[MAPS - 1][e >> 1]);
       }
     }
-    weights_times_values(o, w, vs + (i & 1) * BN * VS, lane);
+    weights_times_values(o, w, V_IN_K ? kt : vs + (i & 1) * BN * VS, lane);
     }
     __syncthreads();
   }
@@ -430,7 +443,7 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
 #pragma unroll
         for (int nt = 0; nt < OT; ++nt) { o[nt][2 * rr] *= corr; o[nt][2 * rr + 1] *= corr; }
       }
-      weights_times_values(o, s, vw, lane);
+      weights_times_values(o, s, V_IN_K ? kw : vw, lane);
     }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -467,7 +480,8 @@ __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const flo
   if (warp < MAPS) {                       // a warp per map: maxima and sums of its parts, merged in a fixed tree
     const float* parts = base + (size_t)warp * (n_splits * WARPS) * (DV + 2);
     float m[(MAX_SPLITS * WARPS + 31) / 32], l[(MAX_SPLITS * WARPS + 31) / 32];
-    float M = A.sink ? 0.f : -INFINITY;
+    const float sv = sink_log2(A, h);
+    float M = A.sink ? sv : -INFINITY;
 #pragma unroll
     for (int k = 0; k < (MAX_SPLITS * WARPS + 31) / 32; ++k) {
       const int i = lane + 32 * k;
@@ -484,7 +498,7 @@ __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const flo
       if (i < n_parts) factor_s[warp][i] = fac;
       L += l[k] * fac;
     }
-    L = co_warp_sum(L) + (A.sink ? ex2(-M) : 0.f);
+    L = co_warp_sum(L) + (A.sink ? ex2(sv - M) : 0.f);
     if (lane == 0) coef_s[warp] = (warp == 0 ? 1.0f : -A.lambda) / L;
   }
   __syncthreads();
@@ -516,6 +530,7 @@ __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const flo
 }  // namespace
 
 CO_EXPORT int coheryn_maps_shape(int* dk, int* dv, int* maps) { *dk = DK; *dv = DV; *maps = MAPS; return 0; }
+CO_EXPORT int coheryn_maps_values_in_keys() { return V_IN_K ? 1 : 0; }
 
 // How the keys a decoded row can see are cut: the keys per split (a multiple of what a CTA's warps take in one round, cut at
 // absolute multiples of itself) and the most splits a row then has (its keys may straddle one boundary more than their
@@ -546,7 +561,8 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
                                           const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B,
                                           int nh, int nkv, int page_size, int window, int chunk, int sink, float scale,
                                           float lambda, int head_norm, float eps, float out_scale, int max_q_len, int max_kv_len,
-                                          int any_single, int any_longer, float* scratch, long scratch_floats, cudaStream_t stream) {
+                                          int any_single, int any_longer, float* scratch, long scratch_floats,
+                                          const float* sink_scores, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nkv <= 0 || nh % nkv) CO_FAIL("attention_maps_bf16: %d heads do not group over %d kv heads", nh, nkv);
   if ((ldq & 7) || (ldo & 1) || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
@@ -555,7 +571,7 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
   const bool decode = any_single && group <= 16;
   MapsArgs A{(const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q,
              kv_lens, nh, nkv, page_size, window, chunk, sink, head_norm, decode ? 1 : 0, 0,
-             scale * 1.4426950408889634f, lambda, eps, out_scale};
+             scale * 1.4426950408889634f, lambda, eps, out_scale, sink_scores};
   if (any_longer || !decode) {
     int visible = max_kv_len;                              // the most keys a row can see
     if (chunk > 0 && chunk < visible) visible = chunk;

@@ -30,7 +30,8 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompil
 # The core library: everything that is not specialised by a compile-time size.
 CORE_SOURCES = ["runtime.cu", "elementwise.cu", "gemm_simt.cu", "attention_simple.cu",
                 "sampling.cu", "gemm_bf16_small.cu", "gemm_tc.cu", "gemm_tc_few.cu", "seeded_fill.cu", "selftest.cu",
-                "block_runner.cu"]
+                "block_runner.cu", "stream_ops.cu"]
+ROUTED_SOURCES = ["routed.cu", "runtime.cu"]
 RECURRENT_SOURCES = ["recurrent.cu", "runtime.cu"]
 VARIANT_SOURCES = ["attention_variants.cu", "runtime.cu"]
 HEADERS = ["common.cuh"]
@@ -248,9 +249,15 @@ def variants_library() -> ctypes.CDLL:
     return load_library("variants", VARIANT_SOURCES)
 
 
-def maps_attention_library(dk: int, dv: int, maps: int) -> ctypes.CDLL:
+def routed_library() -> ctypes.CDLL:
+    """Routing of tokens to experts and matrix products over groups of rows that each meet a matrix of their own (experts,
+    or the heads of an attention with a matrix per head).  Compiled when a model with such a part is first run."""
+    return load_library("routed", ROUTED_SOURCES)
+
+
+def maps_attention_library(dk: int, dv: int, maps: int, values_in_keys: bool = False) -> ctypes.CDLL:
     """The tensor-core kernels of the attention with score maps, compiled for one (channels per map, value channels,
-    maps) when a model needs them."""
+    maps) when a model needs them; ``values_in_keys``: the values are the first ``dv`` channels of the key rows."""
     if dk % 16 or dv % 16 or not 16 <= dk <= 256 or not 16 <= dv <= 256 or maps not in (1, 2):
         raise BuildError(f"the tensor-core attention with score maps takes head sizes 16..256 in steps of 16 and one or "
                          f"two maps, not ({dk}, {dv}, {maps})")
@@ -259,13 +266,17 @@ def maps_attention_library(dk: int, dv: int, maps: int) -> ctypes.CDLL:
         defines["CO_MAPS_BN"] = int(os.environ["COHERYN_MAPS_BN"])
     if os.environ.get("COHERYN_MAPS_MIN_CTAS"):     # ... and the resident CTAs per SM that the prompt kernel's registers must allow
         defines["CO_MAPS_MIN_CTAS"] = int(os.environ["COHERYN_MAPS_MIN_CTAS"])
-    return load_library(f"maps_{dk}_{dv}_{maps}", ["attention_maps_tc.cu", "runtime.cu"], defines)
+    if values_in_keys:
+        defines["CO_MAPS_V_IN_K"] = 1
+    return load_library(f"maps_{dk}_{dv}_{maps}" + ("_vk" if values_in_keys else ""), ["attention_maps_tc.cu", "runtime.cu"], defines)
 
 
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     """Compile everything ahead of time (no GPU needed)."""
     paths = [build_host_library(), build_library("core", CORE_SOURCES), build_library("recurrent", RECURRENT_SOURCES),
-             build_library("variants", VARIANT_SOURCES)]
+             build_library("variants", VARIANT_SOURCES), build_library("routed", ROUTED_SOURCES)]
+    paths.append(build_library("maps_96_64_1_vk", ["attention_maps_tc.cu", "runtime.cu"],
+                               {"CO_MAPS_DK": 96, "CO_MAPS_DV": 64, "CO_MAPS_N": 1, "CO_MAPS_V_IN_K": 1}))
     for dk, dv, maps in ((64, 128, 2), (64, 64, 1)):
         paths.append(build_library(f"maps_{dk}_{dv}_{maps}", ["attention_maps_tc.cu", "runtime.cu"],
                                    {"CO_MAPS_DK": dk, "CO_MAPS_DV": dv, "CO_MAPS_N": maps}))

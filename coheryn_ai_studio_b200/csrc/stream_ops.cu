@@ -1,0 +1,195 @@
+// Kernels on the float32 residual stream of blocks that normalise AFTER the residual add, and of an embedding that
+// adds a row chosen by a hash of (previous token, token):
+//
+//   * embed_pair:         x[t] = table[id_t] * scale + pair[(prev_t * mul_prev + id_t * mul_cur) mod buckets]
+//                         (row `buckets` for the first token of a sequence), optionally x <- x / rms(x) * w;
+//                         prev_t is the token before t in the step, or, for the first token of a request's portion,
+//                         the last token of the request's previous step, kept in a per-request state word;
+//   * store_last_ids:     that state word <- the last token of every request's portion;
+//   * scaled_add_norm:    mode 0: x <- (alpha x + d) / rms(alpha x + d) * w      (a norm after the sum)
+//                         mode 1: x <- x + d / rms(d) * w                        (a normalised summand)
+//                         d the sum of P float32 parts in order; x is written back in float32 and, when asked, as a
+//                         copy in the compute dtype that the next matrix products read;
+//   * gated_table_mul:    out[t, j] = gelu_tanh(z[t, j]) * table[id_t, col0 + j].
+//
+// rms(v) = sqrt(mean(v^2) + eps).  Sums over a row are trees of fixed shape: a row's result does not depend on the
+// other rows of the step.
+#include "common.cuh"
+
+namespace {
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+embed_pair_kernel(const TW* __restrict__ table, const TW* __restrict__ pair, const int* __restrict__ ids,
+                  const int* __restrict__ positions, const int* __restrict__ token_req, const int* __restrict__ cu_q,
+                  const int* __restrict__ state_slots, const int* __restrict__ last_ids, long long mul_prev,
+                  long long mul_cur, long long buckets, float scale, const void* __restrict__ w, int w_dtype, float eps,
+                  float* __restrict__ out, TO* __restrict__ out_cast, int H, int V, int* __restrict__ status) {
+  extern __shared__ __align__(16) float row_s[];
+  __shared__ float scratch[33];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    id = 0;
+  }
+  const TW* prow = nullptr;
+  if (pair) {
+    long long r = buckets;                                  // the first token of a sequence
+    if (positions[t] != 0) {
+      const int b = token_req[t];
+      long long prev = (t == cu_q[b]) ? (long long)last_ids[state_slots[b]] : (long long)ids[t - 1];
+      if (prev < 0 || prev >= V) prev = 0;
+      r = ((prev % buckets) * mul_prev + ((long long)id % buckets) * mul_cur) % buckets;     // multipliers come reduced
+    }
+    prow = pair + (size_t)r * H;
+  }
+  const TW* erow = table + (size_t)id * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float v = co_to_float(erow[j]) * scale;
+    if (prow) v += co_to_float(prow[j]);
+    row_s[j] = v;
+    ss = fmaf(v, v, ss);
+  }
+  float inv = 1.f;
+  if (w) inv = 1.0f / sqrtf(co_block_sum(ss, scratch) / (float)H + eps);
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float v = row_s[j];
+    if (w) v = v * inv * co_load_any(w, w_dtype, j);
+    out[(size_t)t * H + j] = v;
+    if (out_cast) out_cast[(size_t)t * H + j] = co_from_float<TO>(v);
+  }
+}
+
+__global__ void store_last_ids_kernel(const int* __restrict__ ids, const int* __restrict__ cu_q,
+                                      const int* __restrict__ state_slots, int* __restrict__ last_ids, int B) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B && cu_q[b + 1] > cu_q[b]) last_ids[state_slots[b]] = ids[cu_q[b + 1] - 1];
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+scaled_add_norm_kernel(float* __restrict__ x, const float* __restrict__ parts, int P, long part_stride, long row_stride,
+                       float alpha, int mode, const void* __restrict__ w, int w_dtype, float eps,
+                       TO* __restrict__ out_cast, int H) {
+  extern __shared__ __align__(16) float row_s[];
+  __shared__ float scratch[33];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  float* xr = x + t * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float d = 0.f;
+    for (int p = 0; p < P; ++p) d += parts[(size_t)p * part_stride + t * row_stride + j];
+    const float v = mode == 0 ? fmaf(alpha, xr[j], d) : d;
+    row_s[j] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = 1.0f / sqrtf(co_block_sum(ss, scratch) / (float)H + eps);
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float v = row_s[j] * inv * co_load_any(w, w_dtype, j);
+    if (mode != 0) v += xr[j];
+    xr[j] = v;
+    if (out_cast) out_cast[t * H + j] = co_from_float<TO>(v);
+  }
+}
+
+template <typename TZ, typename TW, typename TO>
+__global__ void gated_table_mul_kernel(const TZ* __restrict__ z, long ldz, const TW* __restrict__ table, long ldt, int col0,
+                                       const int* __restrict__ ids, TO* __restrict__ out, int T, int n, int V) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long)T * n) return;
+  const int t = (int)(i / n), j = (int)(i % n);
+  int id = ids[t];
+  if (id < 0 || id >= V) id = 0;
+  out[i] = co_from_float<TO>(co_gelu_tanh(co_to_float(z[(size_t)t * ldz + j])) * co_to_float(table[(size_t)id * ldt + col0 + j]));
+}
+
+}  // namespace
+
+// table [V, H], pair [buckets + 1, H] (null: no pair rows) of one dtype; out float32 [T, H]; out_cast (null or [T, H] of
+// out_dtype); w (null: no norm) [H].  mul_prev and mul_cur must lie in [0, buckets).
+CO_EXPORT int coheryn_embed_pair(const void* table, const void* pair, int table_dtype, const int* ids, const int* positions,
+                                 const int* token_req, const int* cu_q, const int* state_slots, const int* last_ids,
+                                 long long mul_prev, long long mul_cur, long long buckets, float scale, const void* w,
+                                 int w_dtype, float eps, float* out, void* out_cast, int out_dtype, int T, int H, int V,
+                                 int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (pair && (buckets < 1 || mul_prev < 0 || mul_cur < 0 || mul_prev >= buckets || mul_cur >= buckets || buckets > (1ll << 31)))
+    CO_FAIL("embed_pair: multipliers must be reduced modulo the %lld buckets", buckets);
+  if (pair && (!positions || !token_req || !cu_q || !state_slots || !last_ids)) CO_FAIL("embed_pair: the pair rows need the step's layout and the state words");
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) CO_FAIL("embed_pair: a row of %d does not fit in shared memory", H);
+#define GO(TW, TO)                                                                                                     \
+  {                                                                                                                    \
+    auto kern = embed_pair_kernel<TW, TO>;                                                                             \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+    co_launch(kern, dim3(T), dim3(256), smem, stream, (const TW*)table, (const TW*)pair, ids, positions, token_req, cu_q, \
+              state_slots, last_ids, mul_prev, mul_cur, buckets, scale, w, w_dtype, eps, out, (TO*)out_cast, H, V, status); \
+  }
+  const bool cast_bf16 = out_cast && out_dtype == CO_BF16;
+  if (out_cast && out_dtype != CO_BF16 && out_dtype != CO_F32) CO_FAIL("embed_pair: unknown output dtype %d", out_dtype);
+  if (table_dtype == CO_F32) { if (cast_bf16) GO(float, __nv_bfloat16) else GO(float, float) }
+  else if (table_dtype == CO_BF16) { if (cast_bf16) GO(__nv_bfloat16, __nv_bfloat16) else GO(__nv_bfloat16, float) }
+  else CO_FAIL("embed_pair: unknown table dtype %d", table_dtype);
+#undef GO
+  CO_CHECK_LAUNCH("embed_pair");
+  return 0;
+}
+
+CO_EXPORT int coheryn_store_last_ids(const int* ids, const int* cu_q, const int* state_slots, int* last_ids, int B,
+                                     cudaStream_t stream) {
+  if (B <= 0) return 0;
+  co_launch(store_last_ids_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, ids, cu_q, state_slots, last_ids, B);
+  CO_CHECK_LAUNCH("store_last_ids");
+  return 0;
+}
+
+// x float32 [n, H] in place; parts float32: P summands, part p's row t at parts + p * part_stride + t * row_stride.
+CO_EXPORT int coheryn_scaled_add_norm(float* x, const float* parts, int P, long part_stride, long row_stride, float alpha,
+                                      int mode, const void* w, int w_dtype, float eps, void* out_cast, int out_dtype, int n,
+                                      int H, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (!w || P < 1 || (mode != 0 && mode != 1)) CO_FAIL("scaled_add_norm: needs a weight, a summand and mode 0 or 1");
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) CO_FAIL("scaled_add_norm: a row of %d does not fit in shared memory", H);
+#define GO(TO)                                                                                                 \
+  {                                                                                                            \
+    auto kern = scaled_add_norm_kernel<TO>;                                                                    \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    co_launch(kern, dim3(n), dim3(256), smem, stream, x, parts, P, part_stride, row_stride, alpha, mode, w, w_dtype, eps, \
+              (TO*)out_cast, H);                                                                               \
+  }
+  if (out_cast && out_dtype == CO_BF16) GO(__nv_bfloat16)
+  else if (!out_cast || out_dtype == CO_F32) GO(float)
+  else CO_FAIL("scaled_add_norm: unknown output dtype %d", out_dtype);
+#undef GO
+  CO_CHECK_LAUNCH("scaled_add_norm");
+  return 0;
+}
+
+// z [T, n] (row stride ldz) float32 or bfloat16; table [V, ldt] and out [T, n] contiguous of dtype `dtype`.
+CO_EXPORT int coheryn_gated_table_mul(const void* z, int z_dtype, long ldz, const void* table, int dtype, long ldt, int col0,
+                                      const int* ids, void* out, int T, int n, int V, cudaStream_t stream) {
+  if (T <= 0 || n <= 0) return 0;
+  const long total = (long)T * n;
+  dim3 grid((unsigned)((total + 255) / 256));
+#define GO(TZ, TW)                                                                                                \
+  co_launch(gated_table_mul_kernel<TZ, TW, TW>, grid, dim3(256), 0, stream, (const TZ*)z, ldz, (const TW*)table, ldt, col0, \
+            ids, (TW*)out, T, n, V)
+  if (z_dtype == CO_F32 && dtype == CO_F32) GO(float, float);
+  else if (z_dtype == CO_F32 && dtype == CO_BF16) GO(float, __nv_bfloat16);
+  else if (z_dtype == CO_BF16 && dtype == CO_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+  else CO_FAIL("gated_table_mul: unsupported dtypes z=%d table=%d", z_dtype, dtype);
+#undef GO
+  CO_CHECK_LAUNCH("gated_table_mul");
+  return 0;
+}

@@ -33,6 +33,7 @@ def require_gpu() -> None:
 _core = None
 _attn_libs = {}
 _recurrent = None
+_routed = None
 
 
 def core():
@@ -55,7 +56,7 @@ def launch_count() -> int:
 def total_launch_count() -> int:
     """Kernel launches made through every library of this package that is loaded."""
     n = launch_count()
-    for lib in list(_attn_libs.values()) + list(_maps_libs.values()) + [l for l in (_recurrent, _variants) if l is not None]:
+    for lib in list(_attn_libs.values()) + list(_maps_libs.values()) + [l for l in (_recurrent, _variants, _routed) if l is not None]:
         n += int(lib.coheryn_launch_count())
     return n
 
@@ -1161,17 +1162,17 @@ def set_maps_tc(on: bool) -> None:
     MAPS_TC = bool(on)
 
 
-def maps_attention_lib(dk: int, dv: int, maps: int):
-    key = (dk, dv, maps)
+def maps_attention_lib(dk: int, dv: int, maps: int, values_in_keys: bool = False):
+    key = (dk, dv, maps) + ((True,) if values_in_keys else ())
     lib = _maps_libs.get(key)
     if lib is None:
-        lib = build.maps_attention_library(dk, dv, maps)
+        lib = build.maps_attention_library(dk, dv, maps, values_in_keys)
         lib.coheryn_last_error.restype = ctypes.c_char_p
         lib.coheryn_launch_count.restype = ctypes.c_ulonglong
         lib.coheryn_maps_scratch_floats.restype = ctypes.c_long
         got = [ctypes.c_int(), ctypes.c_int(), ctypes.c_int()]
         lib.coheryn_maps_shape(*[ctypes.byref(g) for g in got])
-        if tuple(g.value for g in got) != key:
+        if tuple(g.value for g in got) != key[:3] or bool(lib.coheryn_maps_values_in_keys()) != bool(values_in_keys):
             raise KernelError(f"the attention library was built for {tuple(g.value for g in got)}, not {key}")
         _maps_libs[key] = lib
     return lib
@@ -1180,13 +1181,21 @@ def maps_attention_lib(dk: int, dv: int, maps: int):
 def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
                    num_heads: int, num_kv_heads: int, dk: int, dv: int, maps: int, page_size: int, window: Optional[int],
                    chunk: Optional[int], sink: bool, scale: float, lam: float, head_norm: bool, eps: float,
-                   out_scale: float, force_simple: bool = False) -> None:
+                   out_scale: float, force_simple: bool = False, sink_scores: Optional[torch.Tensor] = None,
+                   values_in_keys: bool = False) -> None:
     """Attention of every token of the step over its request's cache pages of ``group`` with ``maps`` score maps per
     head (output a_0 - lam * a_1 for two), a mask by chunks (``chunk``: position i sees j <= i with i // chunk ==
     j // chunk), by a window or causal, an optional sink term in the softmax's denominator, the head's output divided
     by its root mean square over dv (``head_norm``) and multiplied by ``out_scale``.  q [T, heads * maps * dk],
-    out [T, heads * dv]; float32 arithmetic on either storage type."""
+    out [T, heads * dv]; float32 arithmetic on either storage type.  ``sink_scores`` (float32 [heads]): the sink's score
+    per head instead of 0.  ``values_in_keys``: the values are the first dv channels of the key rows (``v_cache`` is not
+    read)."""
     block_tables = step.block_tables[group]
+    if sink_scores is not None:
+        _dev(sink_scores)
+        assert sink and sink_scores.dtype == torch.float32 and sink_scores.is_contiguous() and sink_scores.numel() == num_heads
+    if values_in_keys:
+        v_cache = k_cache
     _dev(q, out, k_cache, v_cache, block_tables, step.token_req, step.positions)
     _i32(block_tables, "block_tables")
     T = q.shape[0]
@@ -1199,7 +1208,7 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
     if fast:
         # rows that are whole runs of consecutive positions per request, ending at the request's last position
         _i32(step.cu_q, "cu_q"); _i32(step.kv_lens, "kv_lens")
-        lib = maps_attention_lib(dk, dv, maps)
+        lib = maps_attention_lib(dk, dv, maps, values_in_keys)
         B = len(q_lens)
         single = any(n == 1 for n in q_lens) and num_heads // num_kv_heads <= 16
         floats = int(lib.coheryn_maps_scratch_floats(c_int(B), c_int(num_heads), c_int(step.max_kv_len), c_int(window or 0),
@@ -1211,7 +1220,7 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
             c_int(page_size), c_int(window or 0), c_int(chunk or 0), c_int(1 if sink else 0), c_float(scale), c_float(lam),
             c_int(1 if head_norm else 0), c_float(eps), c_float(out_scale), c_int(max(q_lens)), c_int(step.max_kv_len),
             c_int(1 if any(n == 1 for n in q_lens) else 0), c_int(1 if any(n > 1 for n in q_lens) else 0), _ptr(scratch),
-            c_long(floats), _stream()))
+            c_long(floats), _ptr(sink_scores), _stream()))
         return
     lib = variants()
     _check(lib, lib.coheryn_attention_maps(
@@ -1219,4 +1228,225 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
         _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(step.token_req), _ptr(step.positions), c_int(T),
         c_int(num_heads), c_int(num_kv_heads), c_int(dk), c_int(dv), c_int(maps), c_int(page_size), c_int(window or 0),
         c_int(chunk or 0), c_int(1 if sink else 0), c_float(scale), c_float(lam), c_int(1 if head_norm else 0), c_float(eps),
-        c_float(out_scale), _stream()))
+        c_float(out_scale), _ptr(sink_scores), c_int(1 if values_in_keys else 0), _stream()))
+
+
+# ------------------------------------------------------------------------------------
+# Kernels on the residual stream of blocks that normalise after the sum, and an embedding with a hashed pair row
+# (csrc/stream_ops.cu, part of the core library).
+def embed_pair(table: torch.Tensor, pair: Optional[torch.Tensor], step, last_ids: Optional[torch.Tensor], mul_prev: int,
+               mul_cur: int, buckets: int, scale: Optional[float], norm_weight: Optional[torch.Tensor], eps: float,
+               out: torch.Tensor, out_cast: Optional[torch.Tensor], status: torch.Tensor) -> None:
+    """out[t] = table[id_t] * scale + pair[(prev_t * mul_prev + id_t * mul_cur) mod buckets] (row ``buckets`` at position
+    0), then divided by its root mean square and multiplied by ``norm_weight`` when given; float32, with a copy in
+    ``out_cast``'s dtype when given.  prev_t is the step's token before t, or for the first token of a request's portion
+    ``last_ids[state slot of the request]`` (int32 [slots, 1]): the last token of its previous step."""
+    ids = step.token_ids
+    _dev(table, pair, ids, last_ids, norm_weight, out, out_cast, status)
+    _i32(ids, "ids")
+    V, H = table.shape
+    T = ids.numel()
+    assert out.dtype == torch.float32 and out.shape == (T, H) and out.is_contiguous() and table.is_contiguous()
+    if pair is not None:
+        assert pair.shape == (buckets + 1, H) and pair.dtype == table.dtype and pair.is_contiguous()
+        assert last_ids is not None and last_ids.dtype == torch.int32 and last_ids.is_contiguous()
+    if out_cast is not None:
+        assert out_cast.shape == (T, H) and out_cast.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_embed_pair(
+        _ptr(table), _ptr(pair), c_int(_code(table)), _ptr(ids), _ptr(step.positions), _ptr(step.token_req), _ptr(step.cu_q),
+        _ptr(step.state_slots), _ptr(last_ids), ctypes.c_longlong(mul_prev % buckets if pair is not None else 0),
+        ctypes.c_longlong(mul_cur % buckets if pair is not None else 0), ctypes.c_longlong(buckets if pair is not None else 1),
+        c_float(1.0 if scale is None else scale), _ptr(norm_weight), c_int(_code(norm_weight) if norm_weight is not None else F32),
+        c_float(eps), _ptr(out), _ptr(out_cast), c_int(_code(out_cast) if out_cast is not None else F32), c_int(T), c_int(H),
+        c_int(V), _ptr(status), _stream()))
+
+
+def store_last_ids(step, last_ids: torch.Tensor) -> None:
+    """last_ids[state slot of request b] = the last token of b's portion in this step."""
+    _dev(step.token_ids, last_ids)
+    lib = core()
+    _check(lib, lib.coheryn_store_last_ids(_ptr(step.token_ids), _ptr(step.cu_q), _ptr(step.state_slots), _ptr(last_ids),
+                                           c_int(step.num_requests), _stream()))
+
+
+def scaled_add_norm(x: torch.Tensor, parts: torch.Tensor, alpha: float, weight: torch.Tensor, eps: float,
+                    out_cast: Optional[torch.Tensor] = None, normed_summand: bool = False) -> None:
+    """In place on the float32 stream x [n, H], with d the sum of ``parts`` (float32 [n, H] or a stack [P, n, H]):
+    x <- (alpha x + d) / rms(alpha x + d) * weight, or with ``normed_summand`` x <- x + d / rms(d) * weight;
+    ``out_cast`` receives a copy of the new x in its dtype."""
+    _dev(x, parts, weight, out_cast)
+    if parts.dim() == 2:
+        parts = parts.unsqueeze(0)
+    P, n, H = parts.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.shape == (n, H)
+    assert parts.dtype == torch.float32 and parts.stride(2) == 1 and weight.shape == (H,) and weight.is_contiguous()
+    if out_cast is not None:
+        assert out_cast.shape == (n, H) and out_cast.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_scaled_add_norm(
+        _ptr(x), _ptr(parts), c_int(P), c_long(parts.stride(0)), c_long(parts.stride(1)), c_float(alpha),
+        c_int(1 if normed_summand else 0), _ptr(weight), c_int(_code(weight)), c_float(eps), _ptr(out_cast),
+        c_int(_code(out_cast) if out_cast is not None else F32), c_int(n), c_int(H), _stream()))
+
+
+def gated_table_mul(z: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j]."""
+    _dev(z, table, ids, out)
+    _i32(ids, "ids")
+    T, n = z.shape
+    assert z.stride(1) == 1 and table.is_contiguous() and out.is_contiguous() and out.shape == (T, n) and out.dtype == table.dtype
+    assert 0 <= col0 and col0 + n <= table.shape[1]
+    lib = core()
+    _check(lib, lib.coheryn_gated_table_mul(_ptr(z), c_int(_code(z)), c_long(z.stride(0)), _ptr(table), c_int(_code(table)),
+                                            c_long(table.stride(0)), c_int(col0), _ptr(ids), _ptr(out), c_int(T), c_int(n),
+                                            c_int(table.shape[0]), _stream()))
+
+
+# ------------------------------------------------------------------------------------
+# Routed experts and products over groups of rows (csrc/routed.cu, a library of its own that is compiled when a model
+# with such a part is first run).
+def routed():
+    global _routed
+    if _routed is None:
+        lib = build.routed_library()
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        _routed = lib
+    return _routed
+
+
+GROUPED_TC = os.environ.get("COHERYN_GROUPED_TC", "1") != "0"
+
+
+def set_grouped_tc(on: bool) -> None:
+    """Whether bfloat16 grouped products take the tensor cores (the FMA kernel otherwise); for tests and measurements."""
+    global GROUPED_TC
+    GROUPED_TC = bool(on)
+
+
+def route_select(logits: torch.Tensor, correction: Optional[torch.Tensor], n_groups: int, keep: int, top: int,
+                 scale: float):
+    """From router logits (float32 [T, N]) the chosen outputs per token (int32 [T, top], by choice score = softmax +
+    correction, only within the ``keep`` best of ``n_groups`` equal groups of neighbours) and their weights (float32
+    [T, top]: the chosen probabilities over their sum, times ``scale``)."""
+    _dev(logits, correction)
+    _f32(logits, "logits")
+    T, N = logits.shape
+    assert logits.stride(1) == 1
+    if correction is not None:
+        assert correction.shape == (N,) and correction.is_contiguous()
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    lib = routed()
+    _check(lib, lib.coheryn_route_select(_ptr(logits), c_long(logits.stride(0)), _ptr(correction),
+                                         c_int(_code(correction) if correction is not None else F32), c_int(T), c_int(N),
+                                         c_int(n_groups), c_int(keep), c_int(top), c_float(scale), _ptr(ids), _ptr(weights),
+                                         _stream()))
+    return ids, weights
+
+
+class RoutedRows:
+    """The (token, choice) pairs of a step ordered by expert, as ``route_sort`` leaves them on the device."""
+    __slots__ = ("n", "experts", "offsets", "row_of", "token_of", "tile_group", "tile_row0", "n_tiles", "max_tiles")
+
+
+def route_sort(ids: torch.Tensor, experts: int) -> RoutedRows:
+    """Order the pairs whose id names one of the first ``experts`` outputs by expert."""
+    _dev(ids)
+    _i32(ids, "ids")
+    T, top = ids.shape
+    n = T * top
+    lib = routed()
+    bm = int(lib.coheryn_grouped_tile_rows())
+    r = RoutedRows()
+    r.n, r.experts, r.max_tiles = n, experts, n // bm + experts
+    book = torch.empty(experts + 1 + 2 * n + 2 * r.max_tiles + 1, dtype=torch.int32, device=ids.device)
+    o = 0
+    r.offsets = book[o:o + experts + 1]; o += experts + 1
+    r.row_of = book[o:o + n]; o += n
+    r.token_of = book[o:o + n]; o += n
+    r.tile_group = book[o:o + r.max_tiles]; o += r.max_tiles
+    r.tile_row0 = book[o:o + r.max_tiles]; o += r.max_tiles
+    r.n_tiles = book[o:o + 1]
+    _check(lib, lib.coheryn_route_sort(_ptr(ids), c_int(n), c_int(top), c_int(experts), _ptr(r.offsets), _ptr(r.row_of),
+                                       _ptr(r.token_of), _ptr(r.tile_group), _ptr(r.tile_row0), _ptr(r.n_tiles), _stream()))
+    return r
+
+
+def grouped_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: Optional[RoutedRows] = None,
+                   gather: bool = False, a_col: int = 0, c_col: int = 0, epilogue: int = 0,
+                   factor: Optional[torch.Tensor] = None, factor_sigmoid: bool = False) -> None:
+    """Products of groups of rows with a matrix per group; ``w`` [G, N, K].
+
+    With ``rows`` (from ``route_sort``) group g is expert g's rows of the sorted order: row r reads a[token_of[r]] when
+    ``gather`` (else a[r]) and writes out[r].  Without, every row of ``a`` belongs to every group: group g reads columns
+    g * a_col .. g * a_col + K of ``a`` and writes columns g * c_col .. of ``out``.  ``epilogue``: a gated epilogue word
+    (output columns (2j, 2j+1) are gate and up; ``out`` then has N / 2 columns per group).  ``factor`` float32 [rows, G]:
+    every output of (row, group) is multiplied by it (through a sigmoid when ``factor_sigmoid``)."""
+    _dev(a, w, out, factor)
+    G, N, K = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1
+    if factor is not None:
+        _f32(factor, "factor")
+        assert factor.stride(1) == 1 and factor.shape[1] == G
+    lib = routed()
+    M = a.shape[0] if rows is None else rows.n
+    _check(lib, lib.coheryn_grouped_linear(
+        _ptr(a), c_int(_code(a)), c_long(a.stride(0)), c_long(a_col), _ptr(w), c_int(_code(w)), c_long(N * K), _ptr(out),
+        c_int(_code(out)), c_long(out.stride(0)), c_long(c_col),
+        _ptr(rows.token_of) if rows is not None and gather else c_void_p(0),
+        _ptr(rows.tile_group) if rows is not None else c_void_p(0), _ptr(rows.tile_row0) if rows is not None else c_void_p(0),
+        _ptr(rows.offsets) if rows is not None else c_void_p(0), _ptr(rows.n_tiles) if rows is not None else c_void_p(0),
+        c_int(rows.max_tiles if rows is not None else 0), _ptr(factor), c_long(factor.stride(0) if factor is not None else 0),
+        c_int(1 if factor_sigmoid else 0), c_int(M), c_int(N), c_int(K), c_int(G), c_int(epilogue),
+        c_int(1 if GROUPED_TC else 0), _stream()))
+
+
+def route_combine(y: torch.Tensor, h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, rows: RoutedRows,
+                  out: torch.Tensor) -> None:
+    """out[t] = sum over the token's choices in order of weight * (y[row of the pair] for an expert, h[t] for an
+    identity output); y float32 in sorted order, out float32 [T, H]."""
+    _dev(y, h, ids, weights, out)
+    _f32(y, "y"); _f32(out, "out")
+    T, top = ids.shape
+    H = out.shape[1]
+    assert y.stride(1) == 1 and h.stride(1) == 1 and out.is_contiguous() and h.shape == (T, H)
+    lib = routed()
+    _check(lib, lib.coheryn_route_combine(_ptr(y), c_long(y.stride(0)), _ptr(h), c_int(_code(h)), c_long(h.stride(0)), _ptr(ids),
+                                          _ptr(weights), _ptr(rows.row_of), c_int(top), c_int(rows.experts), _ptr(out), c_int(T),
+                                          c_int(H), _stream()))
+
+
+def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rd: int, rank: int, kv_col: Optional[int],
+                   norm_weight: Optional[torch.Tensor], eps: float, positions: torch.Tensor, freq: Optional[torch.Tensor],
+                   rot: int, rot_scale: float, slots: Optional[torch.Tensor], cache: Optional[torch.Tensor], page_size: int,
+                   dtype: torch.dtype):
+    """The step of a latent attention in front of its scores.  ``proj`` float32 [T, ...]: queries head by head as
+    [dim plain | rd rotated] from column 0 and, from column ``kv_col`` (None: a layer that reads another's cache),
+    ``rank`` latent channels and ``rd`` key channels.  Returns (q_plain [T, heads * dim], q_wide [T, heads * (rank + rd)]
+    whose last rd columns per head hold the rotated query part; the first ``rank`` are left for the product that
+    carries the plain part into the latent space), both in ``dtype``; writes the cache rows [latent normalised |
+    rotated key] ([page, 1, page_size, rank + rd]) at ``slots``."""
+    _dev(proj, norm_weight, positions, freq, slots, cache)
+    _f32(proj, "proj")
+    T = proj.shape[0]
+    assert proj.stride(1) == 1
+    write = kv_col is not None
+    if write:
+        _i32(slots, "slots")
+        assert cache.dtype == dtype and cache.is_contiguous() and tuple(cache.shape[1:]) == (1, page_size, rank + rd)
+        assert norm_weight.shape == (rank,) and norm_weight.is_contiguous()
+    if rot:
+        _i32(positions, "positions")
+        assert freq.dtype == torch.float32 and freq.is_contiguous() and tuple(freq.shape) == (rot // 2, 2)
+    q_plain = torch.empty((T, heads * dim), dtype=dtype, device=proj.device)
+    q_wide = torch.empty((T, heads * (rank + rd)), dtype=dtype, device=proj.device)
+    lib = variants()
+    _check(lib, lib.coheryn_latent_prepare(
+        _ptr(proj), _ptr(proj[:, kv_col:]) if write else c_void_p(0), c_long(proj.stride(0)), _ptr(norm_weight) if write else c_void_p(0),
+        c_int(_code(norm_weight) if write else F32), c_float(eps), _ptr(positions), _ptr(freq), c_int(rot), c_float(rot_scale),
+        _ptr(q_plain), _ptr(q_wide), c_int(_CODES[dtype]), _ptr(slots) if write else c_void_p(0),
+        _ptr(cache) if write else c_void_p(0), c_int(T), c_int(heads), c_int(dim), c_int(rd), c_int(rank), c_int(page_size),
+        _stream()))
+    return q_plain, q_wide

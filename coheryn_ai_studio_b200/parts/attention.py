@@ -363,6 +363,143 @@ class MapsAttention(Mixer):
         return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
 
 
+class LatentAttention(Mixer):
+    """Causal attention whose keys and values are two products of ONE latent row per position.
+
+    Per token the layer makes queries of ``heads`` x [``head_dim`` plain | ``rot_dim`` rotated] channels and, when it
+    owns its keys (``own_kv``), ``kv_rank`` latent channels (divided by their root mean square and multiplied by
+    ``dkv.norm``) followed by ``rot_dim`` key channels shared by all heads.  Head h's key at position j is
+    [uk_h c_j | rotated key_j], its value uv_h c_j; the score is (q_plain . uk_h c_j + q_rot . key_j) * ``scale``.
+    The cache holds [c_j | rotated key_j] only, as ONE key head of ``kv_rank + rot_dim`` channels without value rows,
+    and the products with uk and uv move to the query side:
+
+        q_lat_h = uk_h^T q_plain_h,   score = ([q_lat_h | q_rot_h] . [c_j | key_j]) * scale,
+        o_lat_h = sum_j w_j c_j,      head output = uv_h o_lat_h,
+
+    so the attention itself is a multi-query attention over the cached rows whose values are the first ``kv_rank``
+    channels of its keys.  The rotated parts turn over their first ``position.rotary_dim`` channels (the encoding's
+    amplitude multiplies cos and sin; ``scale`` is taken as given).  Options: ``sink`` (one more term exp(sink_h) in the
+    softmax's denominator with a learned score per head, tensor ``sink``, that carries no value) and ``gate`` (head h's
+    output is multiplied by sigmoid(g x)_h, tensor ``g`` [heads, width], the same input as the projections).  A layer
+    without keys of its own reads the rows (latent and rotated key) that an earlier one wrote, with its own uk and uv."""
+
+    output_parts = 1
+
+    def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int,
+                 kv_rank: int, scale: float, eps: float, sink: bool = False, gate: bool = False, own_kv: bool = True,
+                 float32_output: bool = True, position: Optional[Position] = None):
+        super().__init__(runtime)
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.dim, self.rd, self.dv, self.rank = int(head_dim), int(rot_dim), int(v_head_dim), int(kv_rank)
+        if min(self.num_heads, self.dim, self.dv, self.rank) < 1 or self.rd < 0:
+            raise ValueError("a latent attention needs positive head counts and sizes")
+        self.scale, self.eps = float(scale), float(eps)
+        self.sink, self.gate, self.own_kv, self.position = bool(sink), bool(gate), bool(own_kv), position
+        if position is not None and position.rotary_dim > self.rd:
+            raise ValueError(f"{position.rotary_dim} rotated channels do not fit a rotated part of {self.rd}")
+        self.out_dtype = torch.float32 if float32_output else None
+        self.w_in = self.w_uk = self.w_uv = self.w_o = self.w_norm = self.sink_scores = None
+
+    @property
+    def row(self) -> int:
+        """Channels of a cached row."""
+        return self.rank + self.rd
+
+    def cache_requirement(self):
+        return PagedKV(1, self.row, None, 0)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        W, H = self.hidden_size, self.num_heads
+        specs = {"q": TensorSpec((H * (self.dim + self.rd), W)), "uk": TensorSpec((H * self.dim, self.rank)),
+                 "uv": TensorSpec((H * self.dv, self.rank)), "o": TensorSpec((W, H * self.dv))}
+        if self.own_kv:
+            specs["dkv"] = TensorSpec((self.row, W))
+            specs["dkv.norm"] = TensorSpec((self.rank,), role="vector", init="norm")
+        if self.sink:
+            specs["sink"] = TensorSpec((H,), role="vector", init="bias")
+        if self.gate:
+            specs["g"] = TensorSpec((H, W))
+        return specs
+
+    def bind(self, tensors):
+        H = self.num_heads
+        # one product for everything that reads the layer's input: queries, latent + key, gate logits
+        mats = [tensors["q"]] + ([tensors["dkv"]] if self.own_kv else []) + ([tensors["g"]] if self.gate else [])
+        self.w_in = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
+        self.kv_col = H * (self.dim + self.rd) if self.own_kv else None
+        self.gate_col = H * (self.dim + self.rd) + (self.row if self.own_kv else 0)
+        self.w_norm = tensors["dkv.norm"] if self.own_kv else None
+        # uk [heads * dim, rank] applied as uk_h^T: per head a matrix [rank, dim]; uv per head [dv, rank]
+        self.w_uk = tensors["uk"].view(H, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = tensors["uv"].view(H, self.dv, self.rank).contiguous()
+        self.w_o = tensors["o"]
+        self.sink_scores = tensors["sink"].to(torch.float32).contiguous() if self.sink else None
+
+    def output_weights(self):
+        return [self.w_o]
+
+    def _queries(self, x: torch.Tensor, step: StepContext, cache: LayerCache):
+        """(queries in the latent space [T, heads * (rank + rd)], gate logits float32 [T, heads] or None); the rows of
+        the step written to the cache when the layer owns its keys."""
+        Attention._check(cache)
+        if cache.writes != self.own_kv:
+            raise ValueError("a latent attention with a key projection writes its cache; one without reads another's")
+        H = self.num_heads
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        pos = self.position
+        q_plain, q_wide = ops.latent_prepare(
+            proj, H, self.dim, self.rd, self.rank, self.kv_col, self.w_norm, self.eps, step.positions,
+            pos.frequency_pairs() if pos is not None else None, pos.rotary_dim if pos is not None else 0,
+            pos.amplitude if pos is not None else 1.0, step.slots[cache.group] if self.own_kv else None, cache.k,
+            cache.page_size, self.runtime.dtype)
+        ops.grouped_linear(q_plain, self.w_uk, q_wide, a_col=self.dim, c_col=self.row)
+        return q_wide, proj[:, self.gate_col:self.gate_col + H] if self.gate else None
+
+    def _attend(self, q_wide, gates, out, step: StepContext, cache: LayerCache) -> None:
+        H = self.num_heads
+        o_lat = torch.empty((q_wide.shape[0], H * self.rank), dtype=self.runtime.dtype, device=q_wide.device)
+        ops.attention_maps(q_wide, o_lat, cache.k, None, step, cache.group, H, 1, self.row, self.rank, 1, cache.page_size,
+                           None, None, self.sink, self.scale, 0.0, False, self.eps, 1.0, sink_scores=self.sink_scores,
+                           values_in_keys=True)
+        ops.grouped_linear(o_lat, self.w_uv, out, a_col=self.rank, c_col=self.dv, factor=gates, factor_sigmoid=True)
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
+        """The gated heads' outputs in front of the output product into ``outs[0]`` ([T, heads * dv])."""
+        q_wide, gates = self._queries(x, step, cache)
+        self._attend(q_wide, gates, outs[0], step, cache)
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
+    supports_tail = True
+
+    def forward_tail(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> Optional[torch.Tensor]:
+        """The rows of every token go to the cache; only the wanted rows attend (each as a one-token request of
+        ``step.tail``).  A layer that reads another's cache makes the wanted rows' queries only."""
+        rows, tail = step.tail_rows, step.tail
+        if self.own_kv:
+            q_wide, gates = self._queries(x, step, cache)
+            if not tail.num_tokens:
+                return None
+            q_wide = ops.gather_rows(q_wide, rows)
+            gates = ops.gather_rows(gates, rows) if gates is not None else None
+        else:
+            if not tail.num_tokens:
+                return None
+            q_wide, gates = self._queries(ops.gather_rows(x, rows), tail, cache)
+        o = torch.empty((q_wide.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self._attend(q_wide, gates, o, tail, cache)
+        return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
+
+register_mixer("latent_attention", LatentAttention)
 register_mixer("attention_maps", MapsAttention)
 register_mixer("attention", Attention)
 register_mixer("attention_distance_bias", DistanceBiasAttention)

@@ -43,7 +43,13 @@ class PagedKV:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
-    v_head_dim: Optional[int] = None      # values of another head size than keys (None: the same)
+    v_head_dim: Optional[int] = None      # values of another head size than keys (None: the same; 0: no value rows at
+                                          # all, the mixer finds its values inside the key rows)
+
+    @property
+    def value_dim(self) -> int:
+        """Channels of a value row as the pool keeps it."""
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -147,6 +153,19 @@ class PostNormed:
         return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + self.eps) * self.weight.float()
 
 
+@dataclass
+class StreamCopy:
+    """What an arrangement hands on in the place of a pending delta when nothing is pending: the float32 stream is
+    complete, and ``value`` is the same stream in the compute dtype, ready for the next matrix products (the stream
+    itself when the compute dtype is float32).  Blocks that normalise after the sum read the stream itself, so the
+    kernel that finishes a row also writes this copy."""
+
+    value: torch.Tensor
+
+    def resolve(self) -> int:
+        return 0
+
+
 # ------------------------------------------------------------------------------- parts
 class Part:
     # False if ``forward`` waits for the device (reads a result on the host) or launches work whose
@@ -162,6 +181,14 @@ class Part:
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Receive the loaded tensors (same local names); may fuse or re-lay them."""
+
+    def shared_tensors(self) -> Tuple[str, ...]:
+        """Full names of tensors of the MODEL (``ModelSpec.extra_tensors``) that this part reads besides its own: a
+        table that all layers share.  The model hands them to ``bind_shared``."""
+        return ()
+
+    def bind_shared(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
 
 
 class Mixer(Part):
@@ -201,6 +228,19 @@ class Norm(Part):
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedder(Part):
+    """Turns the step's token ids into the float32 stream when that takes more than a table row: ``forward(step,
+    state, out)`` fills ``out`` [T, width] and returns a copy in the compute dtype (or ``out`` itself when that is
+    float32).  ``state_requirement()``: a :class:`FixedState` per request that the embedder keeps (for instance the last
+    token of the request's previous step), or None.  Its tensors are named in full."""
+
+    def state_requirement(self):
+        return None
+
+    def forward(self, step: StepContext, state: Optional[LayerCache], out: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -269,6 +309,7 @@ MIXERS: Dict[str, type] = {}
 FEED_FORWARDS: Dict[str, type] = {}
 NORMS: Dict[str, type] = {}
 POSITIONS: Dict[str, type] = {}
+EMBEDDERS: Dict[str, type] = {}
 ARRANGEMENTS: Dict[str, type] = {}
 
 
@@ -284,6 +325,7 @@ def register_mixer(kind, cls, replace=False): _register(MIXERS, "mixer", kind, c
 def register_feed_forward(kind, cls, replace=False): _register(FEED_FORWARDS, "feed_forward", kind, cls, replace)
 def register_norm(kind, cls, replace=False): _register(NORMS, "norm", kind, cls, replace)
 def register_position(kind, cls, replace=False): _register(POSITIONS, "position", kind, cls, replace)
+def register_embedder(kind, cls, replace=False): _register(EMBEDDERS, "embedder", kind, cls, replace)
 def register_arrangement(kind, cls, replace=False): _register(ARRANGEMENTS, "arrangement", kind, cls, replace)
 
 

@@ -12,7 +12,7 @@ from typing import Dict
 import torch
 
 from .. import ops
-from .base import Arrangement, Part, PostNormed, register_arrangement
+from .base import Arrangement, Part, PostNormed, StreamCopy, register_arrangement
 from .native_block import NativeBlock
 
 
@@ -176,6 +176,73 @@ class SandwichResidual(Arrangement):
         return kept, delta
 
 
+class PostNormResidual(Arrangement):
+    """The norm AFTER the sum: x <- mixer_norm(alpha x + mixer(x)), then x <- feed_forward_norm(alpha x + feed_forward(x));
+    the sub-layers read the stream itself.  Optionally a third sub-layer ``side`` whose output is normalised by itself and
+    added: x <- x + side_norm(side(x)).  The feed-forward (with its norm) and the side (with its norm) may be absent.
+
+    The float32 stream is rewritten in place by the kernel that normalises a row, which also writes the row in the compute
+    dtype for the next matrix products; between blocks that copy travels in the pending delta's place as a
+    :class:`StreamCopy`."""
+
+    SLOTS = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm",
+             "side": "feed_forward", "side_norm": "norm"}
+    OPTIONAL = ("feed_forward", "feed_forward_norm", "side", "side_norm")
+    NAMES = {"mixer": "mixer", "mixer_norm": "post_mixer_norm", "feed_forward": "feed_forward",
+             "feed_forward_norm": "post_feed_forward_norm", "side": "side", "side_norm": "side_norm"}
+
+    def __init__(self, parts, alpha: float = 1.0):
+        super().__init__(parts)
+        self.alpha = float(alpha)
+        for a, b in (("feed_forward", "feed_forward_norm"), ("side", "side_norm")):
+            if (self.slots.get(a) is None) != (self.slots.get(b) is None):
+                raise ValueError(f"postnorm_residual: {a} comes with {b} or not at all")
+
+    def parts(self) -> Dict[str, Part]:
+        names = self.names or self.NAMES
+        return {names[slot]: part for slot, part in self.slots.items()}
+
+    def cache_owner(self):
+        return self.mixer
+
+    def producers(self):
+        return [p for p in (self.mixer, self.feed_forward) if p is not None]     # the side's product is short: never split
+
+    def _input(self, residual, delta):
+        if isinstance(delta, StreamCopy):
+            return delta.value
+        if delta is not None:
+            raise ValueError("postnorm_residual follows blocks that leave nothing pending")
+        dtype = self.mixer.runtime.dtype
+        return residual if dtype == torch.float32 else residual.to(dtype)
+
+    def _rest(self, residual, h, step):
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.post(residual, self.feed_forward.forward(h, step), self.alpha)
+        if self.side is not None:
+            h = self.side_norm.post(residual, self.side.forward(h, step), normed_summand=True)
+        return residual, StreamCopy(h)
+
+    def forward(self, residual, delta, step, cache):
+        h = self._input(residual, delta)
+        h = self.mixer_norm.post(residual, self.mixer.forward(h, step, cache), self.alpha)
+        return self._rest(residual, h, step)
+
+    @property
+    def supports_tail(self):
+        return self.mixer.supports_tail
+
+    def forward_tail(self, residual, delta, step, cache):
+        """The mixer updates its cache for all rows; everything behind it runs for the wanted rows only."""
+        mixed = self.mixer.forward_tail(self._input(residual, delta), step, cache)
+        if mixed is None:
+            return None, None
+        kept = ops.gather_rows(residual, step.tail_rows)
+        h = self.mixer_norm.post(kept, mixed, self.alpha)
+        return self._rest(kept, h, step.tail)
+
+
+register_arrangement("postnorm_residual", PostNormResidual)
 register_arrangement("sandwich_residual", SandwichResidual)
 register_arrangement("prenorm_residual", PreNormResidual)
 register_arrangement("parallel_residual", ParallelResidual)

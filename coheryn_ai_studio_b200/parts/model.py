@@ -11,9 +11,9 @@ import torch
 from .. import ops
 from ..config.spec import ModelSpec
 from ..weights.spec import TensorSpec
-from . import attention, block, feedforward, norm, position, recurrent  # noqa: F401  (register the stock parts)
-from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, LayerCache, Part,
-                   Runtime, StepContext, build_part)
+from . import attention, block, embedding, feedforward, norm, position, recurrent, routed  # noqa: F401  (register the stock parts)
+from .base import (ARRANGEMENTS, EMBEDDERS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, LayerCache, Part,
+                   Runtime, StepContext, StreamCopy, build_part)
 
 
 class DecoderModel:
@@ -42,10 +42,11 @@ class DecoderModel:
                                      f"(slots: {sorted(arr.SLOTS)})")
                 extra = {"position": pos} if role == "mixer" and pos is not None else {}
                 built[slot] = build_part(tables[role], role, part_spec, runtime, **extra)
-            layer = arr(built)
+            layer = arr(built, **dict(ls.arrangement_params))
             layer.names = dict(ls.names) if ls.names is not None else None
             self.layers.append(layer)
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, runtime)
+        self.embedder = build_part(EMBEDDERS, "embedder", spec.embedder, runtime) if spec.embedder is not None else None
         # Outputs go from a layer to the NEXT norm (the following layer's, or the final one),
         # so partial sums may flow only if every norm of the model can add them.
         norms = [n for layer in self.layers for n in layer.norms()] + [self.final_norm]
@@ -54,7 +55,7 @@ class DecoderModel:
                 for part in layer.producers():
                     part.partial_output = True
         self.capturable = all(part.capturable for _, part in self._named_parts()) and all(
-            p.capturable for p in self._positions.values())
+            p.capturable for p in self._positions.values()) and (self.embedder is None or self.embedder.capturable)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.head_bias: Optional[torch.Tensor] = None
@@ -83,7 +84,10 @@ class DecoderModel:
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         """Every tensor the checkpoint must hold, by its full name."""
         s = self.spec
-        specs = {self._matrix_name(s.embedding_name): TensorSpec((s.vocab_size, s.hidden_size))}
+        if self.embedder is not None:
+            specs = dict(self.embedder.tensor_specs())       # it owns the table and names its tensors in full
+        else:
+            specs = {self._matrix_name(s.embedding_name): TensorSpec((s.vocab_size, s.hidden_size))}
         for prefix, part in self._named_parts():
             for local, ts in part.tensor_specs().items():
                 specs[self._join(prefix, local)] = ts
@@ -97,11 +101,18 @@ class DecoderModel:
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
-        self.embedding = tensors[self._matrix_name(s.embedding_name)]
+        if self.embedder is not None:
+            self.embedder.bind({name: tensors[name] for name in self.embedder.tensor_specs() if name in tensors})
+        self.embedding = tensors.get(self._matrix_name(s.embedding_name))
+        if self.embedding is None and (self.embedder is None or s.head_name is None):
+            raise KeyError(self._matrix_name(s.embedding_name))
         for prefix, part in self._named_parts():
             local = {name: tensors[self._join(prefix, name)] for name in part.tensor_specs()
                      if self._join(prefix, name) in tensors}
             part.bind(local)
+            shared = part.shared_tensors()
+            if shared:
+                part.bind_shared({name: tensors[name] for name in shared})
         self.head = tensors[self._matrix_name(s.head_name)] if s.head_name is not None else self.embedding
         self.head_bias = tensors[s.head_bias_name] if s.head_bias_name is not None else None
         self.extra = {name: tensors[name] for name in s.extra_tensors}
@@ -114,7 +125,11 @@ class DecoderModel:
         def need(entry):
             owner = self.layers[entry.layer].cache_owner()
             return owner.cache_requirement() if owner is not None and entry.cache_from is None else None
-        return [need(e) for e in self.spec.schedule]
+        needs = [need(e) for e in self.spec.schedule]
+        # what the model itself keeps per request follows the schedule's entries
+        if self.embedder is not None and self.embedder.state_requirement() is not None:
+            needs.append(self.embedder.state_requirement())
+        return needs
 
     # ------------------------------------------------------------------ forward
     def forward(self, step: StepContext, caches: List[Optional[LayerCache]],
@@ -124,8 +139,12 @@ class DecoderModel:
         T, H = step.num_tokens, self.spec.hidden_size
         step.native = None      # a step object may be run again (warm-up, then capture): on another stream
         residual = torch.empty((T, H), dtype=torch.float32, device=self.runtime.device)
-        ops.embed_gather(self.embedding, step.token_ids, residual, self.status, scale=self.spec.embedding_scale)
         delta = None
+        if self.embedder is not None:
+            own = caches[len(self.spec.schedule)] if len(caches) > len(self.spec.schedule) else None
+            delta = StreamCopy(self.embedder.forward(step, own, residual, self.status))
+        else:
+            ops.embed_gather(self.embedding, step.token_ids, residual, self.status, scale=self.spec.embedding_scale)
         last = len(self.spec.schedule) - 1
         tailed = False
         for i, (entry, cache) in enumerate(zip(self.spec.schedule, caches)):
@@ -141,7 +160,7 @@ class DecoderModel:
             else:
                 residual, delta = layer.forward(residual, delta, step, cache)
             if self.layer_observer is not None:
-                if delta is None:
+                if delta is None or isinstance(delta, StreamCopy):
                     out = residual
                 elif hasattr(delta, "resolve"):      # a summand that is normalised before it is added
                     out = residual + delta.resolve()
@@ -151,6 +170,8 @@ class DecoderModel:
         R = logit_rows.numel()
         if R == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
+        if isinstance(delta, StreamCopy):       # nothing is pending
+            delta = None
         h = self.final_norm.forward(residual, delta, rows=None if tailed else logit_rows)
         logits = ops.linear(h, self.head, out_dtype=torch.float32)
         if self.spec.logit_scale is not None or self.head_bias is not None or self.spec.logit_softcap is not None:

@@ -41,6 +41,16 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows=rows)
         return out
 
+    def post(self, residual, delta, alpha: float = 1.0, normed_summand: bool = False):
+        """The norm AFTER the sum, in place on the float32 stream: residual <- (alpha residual + delta) / rms(..) * w; with
+        ``normed_summand`` residual <- residual + delta / rms(delta) * w instead.  ``delta``: float32 [T, H] or a stack
+        [P, T, H] of partial sums.  Returns the new stream in the compute dtype (the stream itself when that is float32)."""
+        if delta.dtype != torch.float32:
+            raise ValueError("a norm after the sum takes its summand in float32")
+        cast = None if self.runtime.dtype == torch.float32 else torch.empty(residual.shape, dtype=self.runtime.dtype, device=residual.device)
+        ops.scaled_add_norm(residual, delta, alpha, self.weight, self.eps, cast, normed_summand=normed_summand)
+        return residual if cast is None else cast
+
 
 def apply_post_normed(residual, delta: PostNormed, weight, eps: float, out, rows=None) -> None:
     """residual += delta.value / rms(delta.value) * delta.weight (without ``rows``); ``out`` = the normalised sum times
