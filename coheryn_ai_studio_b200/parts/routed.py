@@ -58,7 +58,7 @@ class RoutedExperts(FeedForward):
         g, u, d = self.names
         specs = {"router": TensorSpec((self.outputs, W))}
         if self.correction:
-            specs["correction"] = TensorSpec((self.outputs,), role="vector", init="bias")
+            specs["correction"] = TensorSpec((self.outputs,), role="vector", init="normal")
         for e in range(self.experts):
             p = f"{self.prefix}{e}."
             specs[p + g], specs[p + u], specs[p + d] = TensorSpec((F, W)), TensorSpec((F, W)), TensorSpec((W, F))

@@ -177,8 +177,11 @@ def token_side(x, tokens, W, p, index, dim, eps, rounder=None):
     return x + rms(y, eps) * W[p + "norm"]
 
 
-def forward(tokens, W, cfg, positions=None, rounder=None, layer_outputs=None):
-    """Logits [T, vocab] of a whole sequence; ``layer_outputs`` (a list) receives the stream after every layer."""
+def forward(tokens, W, cfg, positions=None, rounder=None, layer_outputs=None, rounded=False):
+    """Logits [T, vocab] of a whole sequence; ``layer_outputs`` (a list) receives the stream after every layer.
+    ``rounded``: the twin that rounds to bfloat16 what an engine computing in 16 bits hands from kernel to kernel."""
+    if rounded:
+        rounder = round_bf16
     rd = rounder or (lambda z: z)
     eps, alpha = cfg["norm"]["eps"], cfg.get("postln_alpha", 1.0)
     positions = list(range(len(tokens))) if positions is None else positions

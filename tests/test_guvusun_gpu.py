@@ -1,0 +1,627 @@
+"""The Guvusun decoder on the GPU against the plain implementation (``plain_guvusun.py``): each mechanism's kernels
+alone, then whole models through the step function, the cache and the scheduler, in float32 and in bfloat16."""
+import math
+import types
+
+import numpy as np
+import pytest
+import torch
+
+import guvusun_cases as gc
+import plain_guvusun as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["G1", "G2", "G3"]
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("guvusun")
+    return {n: gc.make_folder(base, n) for n in NAMES}
+
+
+@pytest.fixture(scope="module")
+def models(folders):
+    from coheryn_ai_studio_b200.engine import load_model
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            cache[(name, dtype)] = load_model(folders[name], dtype)[1]
+        return cache[(name, dtype)]
+    return get
+
+
+def vocab(name):
+    return gc.CASES[name][0]["vocab"]
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a), dtype=dtype).to(DEV)
+
+
+def bf(a):
+    """A float64 array rounded to bfloat16 values."""
+    return plain.round_bf16(np.asarray(a, dtype=np.float64))
+
+
+def host(t):
+    return t.float().cpu().numpy().astype(np.float64)
+
+
+class Rows:
+    """A hand-made paged cache of key rows for one latent attention: requests of given lengths whose pages are handed out in
+    a scrambled order, and steps over any runs of their positions."""
+
+    def __init__(self, lengths, channels, page, dtype, seed=0, slots=None):
+        from coheryn_ai_studio_b200.parts.base import LayerCache
+        self.page = page
+        pages = [-(-n // page) for n in lengths]
+        order = np.random.default_rng(seed).permutation(sum(pages) + 3)
+        self.tables = np.full((len(lengths), max(pages) + 1), -1, dtype=np.int32)
+        at = 0
+        for r, n in enumerate(pages):
+            self.tables[r, :n] = order[at:at + n]
+            at += n
+        self.k = torch.full((len(order), 1, page, channels), 7.0, dtype=dtype, device=DEV)     # noise where nothing is written
+        self.state_slots = list(range(len(lengths))) if slots is None else slots
+        self.writer = LayerCache(kind="paged", group=0, page_size=page, k=self.k, v=None, writes=True)
+        self.reader = LayerCache(kind="paged", group=0, page_size=page, k=self.k, v=None, writes=False)
+
+    def step(self, runs, ids=None):
+        """``runs``: (request, first position, tokens) in batch order; the requests' lengths are first + tokens."""
+        req = np.concatenate([np.full(n, i) for i, (_, _, n) in enumerate(runs)]).astype(np.int32)
+        pos = np.concatenate([np.arange(s, s + n) for _, s, n in runs]).astype(np.int32)
+        cu = np.concatenate([[0], np.cumsum([n for _, _, n in runs])]).astype(np.int32)
+        tables = np.stack([self.tables[r] for r, _, _ in runs])
+        slots = np.concatenate([self.tables[r][np.arange(s, s + n) // self.page] * self.page + np.arange(s, s + n) % self.page
+                                for r, s, n in runs]).astype(np.int32)
+        kv = [s + n for _, s, n in runs]
+        return types.SimpleNamespace(
+            num_requests=len(runs), num_tokens=int(cu[-1]), token_req=dev(req, torch.int32), positions=dev(pos, torch.int32),
+            cu_q=dev(cu, torch.int32), kv_lens=dev(kv, torch.int32), block_tables=[dev(tables, torch.int32)],
+            slots=[dev(slots, torch.int32)], q_lens=[n for _, _, n in runs], max_q_len=max(n for _, _, n in runs),
+            max_kv_len=max(kv), prior_positions_settled=True, token_ids=dev(ids, torch.int32) if ids is not None else None,
+            state_slots=dev([self.state_slots[r] for r, _, _ in runs], torch.int32), tail=None, tail_rows=None)
+
+
+def step_of(runs, ids, slots):
+    """A step without pages: ``runs`` as above; ``slots``: the state slot of every request."""
+    req = np.concatenate([np.full(n, i) for i, (_, _, n) in enumerate(runs)]).astype(np.int32)
+    pos = np.concatenate([np.arange(s, s + n) for _, s, n in runs]).astype(np.int32)
+    cu = np.concatenate([[0], np.cumsum([n for _, _, n in runs])]).astype(np.int32)
+    return types.SimpleNamespace(
+        num_requests=len(runs), num_tokens=int(cu[-1]), token_req=dev(req, torch.int32), positions=dev(pos, torch.int32),
+        cu_q=dev(cu, torch.int32), token_ids=dev(ids, torch.int32), state_slots=dev([slots[r] for r, _, _ in runs], torch.int32))
+
+
+# ------------------------------------------------------------------------------ the embedding
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("buckets,mul_prev,mul_cur,width", [(257, 31, 5, 64), (97, 1000003, 389, 100), (1, 3, 4, 8), (8191, 0, 1, 520)])
+def test_pair_row_embedding_in_portions(dtype, buckets, mul_prev, mul_cur, width):
+    """Two sequences cut into portions down to one token: the token before a portion's first comes from the request's state
+    word, which a request that ended leaves to the next user of its slot (who starts with the last row of the pair table)."""
+    from coheryn_ai_studio_b200 import ops
+    rng = np.random.default_rng(buckets)
+    V, eps = 150, 1e-5
+    W = {"embed": bf(rng.normal(size=(V, width))), "bigram": bf(rng.normal(size=(buckets + 1, width))),
+         "embed.norm": bf(1 + 0.2 * rng.normal(size=width))}
+    cfg = {"embedding": {"bigram": {"buckets": buckets, "mul_prev": mul_prev, "mul_cur": mul_cur}}, "norm": {"eps": eps}}
+    seqs = [rng.integers(0, V, size=n).tolist() for n in (41, 17, 9)]
+    want = [plain.embedding(s, W, cfg) for s in seqs]
+    last = torch.full((2, 1), 77, dtype=torch.int32, device=DEV)                  # noise: a first token must not read it
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    table, pair, norm = dev(W["embed"], dtype), dev(W["bigram"], dtype), dev(W["embed.norm"])
+    # requests 0 and 1 share the steps; request 2 then takes request 1's slot
+    plan = [[(0, 0, 7), (1, 0, 1)], [(0, 7, 1), (1, 1, 2)], [(1, 3, 14), (0, 8, 2)], [(0, 10, 31)], [(2, 0, 3)], [(2, 3, 1)], [(2, 4, 5)]]
+    for runs in plan:
+        ids = np.concatenate([seqs[r][s:s + n] for r, s, n in runs])
+        step = step_of(runs, ids, slots=[0, 1, 1])
+        out = torch.empty((len(ids), width), dtype=torch.float32, device=DEV)
+        cast = torch.empty((len(ids), width), dtype=dtype, device=DEV) if dtype != torch.float32 else None
+        ops.embed_pair(table, pair, step, last, mul_prev, mul_cur, buckets, None, norm, eps, out, cast, status)
+        ops.store_last_ids(step, last)
+        ref = np.concatenate([want[r][s:s + n] for r, s, n in runs])
+        assert np.abs(host(out) - ref).max() < 1e-5 * max(1.0, np.abs(ref).max()), runs
+        if cast is not None:
+            assert np.abs(host(cast) - ref).max() < 0.01 * max(1.0, np.abs(ref).max())
+    assert int(status.item()) == 0
+
+
+# ------------------------------------------------------------------------------ norms on the stream
+@pytest.mark.parametrize("rows,width,parts", [(5, 64, 1), (70, 100, 3), (9, 256, 2), (3, 8192, 1), (300, 80, 2)])
+@pytest.mark.parametrize("alpha", [1.0, 2.5])
+def test_norm_after_the_sum_and_normalised_summand(rows, width, parts, alpha):
+    from coheryn_ai_studio_b200 import ops
+    rng = np.random.default_rng(rows + width)
+    x, d, w, eps = rng.normal(size=(rows, width)), rng.normal(size=(parts, rows, width)) * 3, 1 + 0.3 * rng.normal(size=width), 1e-5
+    for summand in (False, True):
+        xs, cast = dev(x), torch.empty((rows, width), dtype=torch.bfloat16, device=DEV)
+        ops.scaled_add_norm(xs, dev(d), alpha, dev(w), eps, cast, normed_summand=summand)
+        want = x + plain.rms(d.sum(0), eps) * w if summand else plain.rms(alpha * x + d.sum(0), eps) * w
+        assert np.abs(host(xs) - want).max() < 2e-5 * max(1.0, np.abs(want).max()), summand
+        assert np.abs(host(cast) - want).max() < 0.01 * max(1.0, np.abs(want).max())
+
+
+# ------------------------------------------------------------------------------ routed experts
+def router_weights(rng, width, outputs, correction_scale):
+    return {"router": bf(rng.normal(size=(outputs, width)) * 0.3), "correction": bf(rng.normal(size=outputs) * correction_scale)}
+
+
+@pytest.mark.parametrize("outputs,identity,groups,keep,top", [(8, 2, 4, 2, 3), (6, 0, 1, 1, 1), (6, 1, 3, 2, 2), (3, 0, 1, 1, 3),
+                                                              (12, 4, 3, 2, 8), (64, 0, 8, 3, 6), (40, 8, 2, 1, 20), (5, 0, 5, 2, 2)])
+@pytest.mark.parametrize("correction_scale", [0.05, 5.0])
+def test_router_choices_and_weights(outputs, identity, groups, keep, top, correction_scale):
+    """The chosen outputs equal the plain router's, in its order, and the weights agree; with corrections of size 5 most
+    choice scores are negative, so a group that is not kept must count as minus infinity, not as zero."""
+    from coheryn_ai_studio_b200 import ops
+    rng = np.random.default_rng(outputs * 10 + top)
+    width, T = 48, 257
+    W = router_weights(rng, width, outputs, correction_scale)
+    h = rng.normal(size=(T, width))
+    router = {"experts": outputs - identity, "identity": identity, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}
+    want_ids, want_w = plain.route(h, W, "", router)
+    logits = dev(h @ W["router"].T)
+    ids, weights = ops.route_select(logits, dev(W["correction"]), groups, keep, top, 2.5)
+    ids, weights = ids.cpu().numpy(), host(weights)
+    # a float32 softmax can order two nearly equal scores the other way: such rows are compared as sets
+    exact = (ids == want_ids).all(-1)
+    assert exact.mean() > 0.97
+    for t in np.nonzero(~exact)[0]:
+        assert sorted(ids[t]) == sorted(want_ids[t]) or np.sort(want_w[t])[0] < 1e-3 * 2.5, t
+    assert np.abs(weights[exact] - want_w[exact]).max() < 1e-5
+    assert np.abs(weights.sum(-1) - 2.5).max() < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,ff,experts,identity,groups,keep,top,T", [(64, 32, 6, 2, 4, 2, 3, 300), (100, 50, 5, 1, 3, 2, 2, 77),
+                                                                          (64, 48, 4, 0, 1, 1, 1, 1), (128, 64, 8, 0, 2, 1, 4, 9),
+                                                                          (40, 30, 3, 0, 1, 1, 3, 130)])
+def test_routed_experts_equal_the_plain_experts(dtype, width, ff, experts, identity, groups, keep, top, T):
+    """The part alone: tokens of a step sorted by expert (an expert can get more rows than one tile holds, or none at all),
+    grouped products, identity experts, the weighted sum.  A token's result does not depend on the other tokens."""
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.routed import RoutedExperts
+    rng = np.random.default_rng(width + T)
+    W = router_weights(rng, width, experts + identity, 0.1)
+    for e in range(experts):
+        W[f"e{e}.gate"], W[f"e{e}.up"] = bf(rng.normal(size=(ff, width)) * 0.2), bf(rng.normal(size=(ff, width)) * 0.2)
+        W[f"e{e}.down"] = bf(rng.normal(size=(width, ff)) * 0.2)
+    h = bf(rng.normal(size=(T, width)))
+    mlp = {"router": {"experts": experts, "identity": identity, "top": top, "scale": 1.5, "groups": {"count": groups, "keep": keep}}}
+    want = plain.routed_experts(h, W, "", mlp, rounder=bf if dtype == torch.bfloat16 else None)
+    part = RoutedExperts(Runtime(dtype, torch.device(DEV)), width, ff, experts, top, identity, groups, keep, 1.5)
+    part.bind({k: dev(v, torch.float32 if k == "correction" else dtype) for k, v in W.items()})
+    got = host(part.forward(dev(h, dtype), None))
+    tol = 2e-5 if dtype == torch.float32 else 0.02
+    chosen, _ = plain.route(h, W, "", mlp["router"])
+    flipped = ~(np.sort(part.choose(dev(h, dtype))[0].cpu().numpy(), -1) == np.sort(chosen, -1)).all(-1)
+    assert flipped.mean() < 0.03                       # a near tie that float32 decides the other way
+    ok = ~flipped
+    assert np.abs(got[ok] - want[ok]).max() < tol * max(1.0, np.abs(want).max())
+    if T > 4:                                          # three rows alone: the same bits as among the others
+        alone = host(part.forward(dev(h[1:4], dtype), None))
+        assert np.array_equal(alone, got[1:4])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,dim,layers,index", [(64, 8, 3, 1), (100, 5, 2, 0), (128, 16, 4, 3)])
+def test_token_input_of_a_layer(dtype, width, dim, layers, index):
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.norm import RMSNorm
+    from coheryn_ai_studio_b200.parts.routed import TokenTableGate
+    rng = np.random.default_rng(width)
+    V, T, eps = 90, 37, 1e-5
+    W = {"side.embed": bf(rng.normal(size=(V, layers * dim))), "gate": bf(rng.normal(size=(dim, width)) * 0.3),
+         "proj": bf(rng.normal(size=(width, dim)) * 0.3), "norm": bf(1 + 0.2 * rng.normal(size=width))}
+    x, tokens = rng.normal(size=(T, width)), rng.integers(0, V, size=T)
+    want = plain.token_side(x, tokens, W, "", index, dim, eps, rounder=bf if dtype == torch.bfloat16 else None)
+    rt = Runtime(dtype, torch.device(DEV))
+    part = TokenTableGate(rt, width, dim, "side.embed", index * dim, V)
+    part.bind({"gate": dev(W["gate"], dtype), "proj": dev(W["proj"], dtype)})
+    part.bind_shared({"side.embed": dev(W["side.embed"], dtype)})
+    norm = RMSNorm(rt, width, eps, tensor="")
+    norm.bind({"": dev(W["norm"])})
+    stream = dev(x)
+    h = norm.post(stream, part.forward(dev(x, dtype), types.SimpleNamespace(token_ids=dev(tokens, torch.int32))), normed_summand=True)
+    tol = 2e-5 if dtype == torch.float32 else 0.03
+    assert np.abs(host(stream) - want).max() < tol * max(1.0, np.abs(want).max())
+    assert np.abs(host(h) - want).max() < max(tol, 0.01) * max(1.0, np.abs(want).max())
+
+
+# ------------------------------------------------------------------------------ latent attention
+def mixer_weights(rng, width, m, own=True, std=0.25):
+    H, dim, rd, vd, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    W = {"q": bf(rng.normal(size=(H * (dim + rd), width)) * std), "uk": bf(rng.normal(size=(H * dim, r)) * std),
+         "uv": bf(rng.normal(size=(H * vd, r)) * std), "o": bf(rng.normal(size=(width, H * vd)) * std),
+         "sink": bf(rng.normal(size=H)), "g": bf(rng.normal(size=(H, width)) * std)}
+    if own:
+        W["dkv"], W["dkv.norm"] = bf(rng.normal(size=(r + rd, width)) * std), bf(1 + 0.2 * rng.normal(size=r))
+    return W
+
+
+def make_mixer(m, width, eps, dtype, W, own=True):
+    from coheryn_ai_studio_b200.parts.attention import LatentAttention
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.position import ComputedRope
+    rt = Runtime(dtype, torch.device(DEV))
+    rot = m["rot"]
+    pos = ComputedRope(rt, rotary_dim=rot["dims"], theta=rot["base"], scaling=rot.get("scaling"))
+    mixer = LatentAttention(rt, width, m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["scale"], eps, sink=True,
+                            gate=True, own_kv=own, position=pos)
+    mixer.bind({k: dev(v, torch.float32 if k in ("sink", "dkv.norm") else dtype) for k, v in W.items()})
+    return mixer
+
+
+def shape(heads, dim, rot_dim, vdim, kv_rank, rot, scale=0.2):
+    return {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": scale, "rot": rot}
+
+
+YARN = {"dims": 16, "base": 1000.0, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}}
+MIXERS = [
+    (shape(4, 16, 16, 16, 32, YARN), 64, 16),                                   # rows of 48 channels: the tensor cores
+    (shape(20, 16, 16, 8, 48, {"dims": 8, "base": 10000.0}), 128, 8),           # twenty heads over the one row; half the part turns
+    (shape(3, 12, 6, 10, 20, {"dims": 6, "base": 77.0}), 100, 16),              # nothing divides: the float32-arithmetic kernels
+    (shape(2, 40, 32, 24, 224, {"dims": 32, "base": 50.0}), 80, 16),            # rows of 256 channels
+    (shape(1, 8, 4, 8, 300, {"dims": 4, "base": 9.0}), 64, 4),                  # a latent wider than any tile
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,width,page", MIXERS)
+def test_latent_attention_in_portions_and_decoded(dtype, m, width, page):
+    """Two sequences at once, cut into portions (down to one token, which takes the decoding kernels) across pages and
+    tiles, equal to the plain mixer over the whole sequences; a second mixer of other head counts and sizes reads the rows
+    the first one cached."""
+    rng = np.random.default_rng(m["heads"] * 100 + m["kv_rank"])
+    eps, lengths = 1e-5, [150, 83]
+    m2 = dict(m, heads=max(1, m["heads"] // 2), dim=m["dim"] + 8, vdim=m["vdim"] + 16, scale=0.15)
+    W1, W2 = mixer_weights(rng, width, m), mixer_weights(rng, width, m2, own=False)
+    a, b = make_mixer(m, width, eps, dtype, W1), make_mixer(m2, width, eps, dtype, W2, own=False)
+    rd = bf if dtype == torch.bfloat16 else None
+    seqs = []
+    for n in lengths:
+        h = bf(rng.normal(size=(n, width)))
+        y1, kept = plain.latent_attention(h, range(n), W1, "", m, eps, rounder=rd)
+        y2, _ = plain.latent_attention(h * 0.5, range(n), W2, "", m2, eps, shared=kept, rounder=rd)
+        seqs.append((h, y1, y2))
+    cache = Rows(lengths, m["kv_rank"] + m["rot_dim"], page, dtype, seed=width)
+    cuts = [[70, 1, 1, 2, 39, 1, 36], [1, 1, 30, 17, 2, 1, 31]]
+    at = [0, 0]
+    tol = 3e-5 if dtype == torch.float32 else 0.03
+    for n0, n1 in zip(*cuts):
+        step = cache.step([(0, at[0], n0), (1, at[1], n1)])
+        h = np.concatenate([seqs[0][0][at[0]:at[0] + n0], seqs[1][0][at[1]:at[1] + n1]])
+        for mixer, which, cache_view, scale in ((a, 1, cache.writer, 1.0), (b, 2, cache.reader, 0.5)):
+            got = host(mixer.forward(dev(h * scale, dtype), step, cache_view))
+            want = np.concatenate([seqs[0][which][at[0]:at[0] + n0], seqs[1][which][at[1]:at[1] + n1]])
+            assert np.abs(got - want).max() < tol * max(1.0, np.abs(want).max()), (which, at, n0, n1, np.abs(got - want).max())
+        at = [at[0] + n0, at[1] + n1]
+    assert at == lengths
+
+
+@pytest.mark.parametrize("tensor_cores", [True, False])
+@pytest.mark.parametrize("m,width,page", [MIXERS[0], MIXERS[1], (shape(2, 24, 32, 16, 64, {"dims": 32, "base": 10000.0}), 64, 8)])
+def test_one_key_that_stands_out_far_back_and_at_the_borders(tensor_cores, m, width, page):
+    """The slowest-turning pair of the rotated key part of ONE position and of every query carries a large component, so a
+    row that may see that position puts nearly all its weight there: at position 0, on both sides of page and tile borders,
+    and hundreds of positions back; read in a first portion (rows before the key must not see it), in a second portion and
+    decoded alone.  Losing the key, or seeing it one row early, changes the rows completely."""
+    from coheryn_ai_studio_b200 import ops
+    rng = np.random.default_rng(m["heads"])
+    eps, n, dtype = 1e-5, 420, torch.bfloat16
+    H, dim, rdim, r = m["heads"], m["dim"], m["rot_dim"], m["kv_rank"]
+    pair = m["rot"]["dims"] // 2 - 1                                    # the slowest-turning pair: channels (pair, pair + dims/2)
+    W = mixer_weights(rng, width, m, std=0.05)
+    W["dkv"][r + pair] = 0.0; W["dkv"][r + pair, 0] = 6.0              # input channel 0 marks the key
+    for hd in range(H):
+        W["q"][hd * (dim + rdim) + dim + pair] = 0.0
+        W["q"][hd * (dim + rdim) + dim + pair, 1] = 6.0                 # input channel 1 is 1 in every row: all rows ask for it
+    W["sink"][:] = -3.0
+    mixer = make_mixer(m, width, eps, dtype, W)
+    ops.set_maps_tc(tensor_cores)
+    try:
+        for marked in (0, 5, page - 1, page, 63, 64, 127, 128):
+            h = bf(rng.normal(size=(n, width)) * 0.3)
+            h[:, 0], h[:, 1] = 0.0, 1.0
+            h[marked, 0] = 1.0
+            want, (c, _) = plain.latent_attention(h, range(n), W, "", m, eps, rounder=bf)
+            cache = Rows([n], r + rdim, page, dtype, seed=marked)
+            got, at = [], 0
+            for portion in (max(marked + 2, 130), 401 - max(marked + 2, 130), 1, 1, 1, 1, 1, 1, 1, 1, 1, 9, 1):
+                got.append(host(mixer.forward(dev(h[at:at + portion], dtype), cache.step([(0, at, portion)]), cache.writer)))
+                at += portion
+            got = np.concatenate(got)
+            assert at == n and np.abs(got - want).max() < 0.04 * max(1.0, np.abs(want).max()), (marked, np.abs(got - want).max())
+            # the setup itself: with the key the rows differ from those without it by far more than the tolerance
+            h2 = h.copy(); h2[marked, 0] = 0.0
+            without = plain.latent_attention(h2, range(n), W, "", m, eps, rounder=bf)[0]
+            for row in (marked + 1, 300, 400, 401, 409, 419):
+                assert np.abs(want[row] - without[row]).max() > 0.3 * np.abs(want).max(), (marked, row, "the key does not stand out")
+            if marked:
+                assert np.abs(want[marked - 1] - without[marked - 1]).max() == 0.0
+    finally:
+        ops.set_maps_tc(True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_sink_takes_weight_per_head_and_carries_no_value(dtype):
+    """A sink far above every score empties its head's output; one far below changes nothing; in between it counts once."""
+    rng = np.random.default_rng(9)
+    m, width, eps, n = shape(4, 16, 16, 16, 32, YARN), 64, 1e-5, 90
+    W = mixer_weights(rng, width, m)
+    W["sink"][:] = [30.0, -30.0, 0.5, -1.0]
+    W["g"][:] = 0.0                                                  # every gate is one half
+    h = bf(rng.normal(size=(n, width)))
+    want = plain.latent_attention(h, range(n), W, "", m, eps, rounder=bf if dtype == torch.bfloat16 else None)[0]
+    Wn = dict(W, sink=np.array([30.0, -60.0, -60.0, -60.0]))
+    no_sink = plain.latent_attention(h, range(n), Wn, "", m, eps)[0]
+    assert np.abs(want - no_sink).max() > 0.05 * np.abs(want).max()      # the middle sinks matter
+    mixer = make_mixer(m, width, eps, dtype, W)
+    cache = Rows([n], 48, 16, dtype)
+    got = np.concatenate([host(mixer.forward(dev(h[:70], dtype), cache.step([(0, 0, 70)]), cache.writer))]
+                         + [host(mixer.forward(dev(h[t:t + 1], dtype), cache.step([(0, t, 1)]), cache.writer)) for t in range(70, n)])
+    assert np.abs(got - want).max() < (3e-5 if dtype == torch.float32 else 0.03) * max(1.0, np.abs(want).max())
+    # head 0 alone: its sink swallows everything, so the output without heads 1..3 is nothing
+    o = torch.empty((n, 4 * 16), dtype=dtype, device=DEV)
+    cache2 = Rows([n], 48, 16, dtype)
+    mixer.forward_open(dev(h, dtype), cache2.step([(0, 0, n)]), cache2.writer, [o])
+    assert np.abs(host(o)[:, :16]).max() < 1e-4 and np.abs(host(o)[:, 16:]).max() > 0.05
+
+
+def test_angles_at_a_position_beyond_a_million():
+    """Rotated query parts and the cached key part at position 1,000,003 against float64 angles."""
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.position import ComputedRope
+    rng = np.random.default_rng(4)
+    heads, dim, rd, rank, page = 3, 8, 16, 24, 16
+    rot = YARN
+    pos = ComputedRope(Runtime(torch.float32, torch.device(DEV)), rotary_dim=16, theta=rot["base"], scaling=rot["scaling"])
+    T, p0 = 5, 1_000_003
+    proj = rng.normal(size=(T, heads * (dim + rd) + rank + rd))
+    cache = torch.zeros((2, 1, page, rank + rd), device=DEV)
+    w = 1 + 0.2 * rng.normal(size=rank)
+    _, q_wide = ops.latent_prepare(dev(proj), heads, dim, rd, rank, heads * (dim + rd), dev(w), 1e-5,
+                                   dev(np.arange(p0, p0 + T), torch.int32), pos.frequency_pairs(), 16, pos.amplitude,
+                                   dev(np.arange(16, 16 + T), torch.int32), cache, page, torch.float32)
+    q = proj[:, :heads * (dim + rd)].reshape(T, heads, dim + rd)
+    want_q = plain.rotate(q[..., dim:], range(p0, p0 + T), rot)
+    got_q = host(q_wide).reshape(T, heads, rank + rd)[..., rank:]
+    assert np.abs(got_q - want_q).max() < 3e-6 * np.abs(want_q).max()
+    kv = proj[:, heads * (dim + rd):]
+    want_row = np.concatenate([plain.rms(kv[:, :rank], 1e-5) * w, plain.rotate(kv[:, rank:], range(p0, p0 + T), rot)], axis=-1)
+    assert np.abs(host(cache)[1, 0, :T] - want_row).max() < 3e-6 * np.abs(want_row).max()
+
+
+# ------------------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_prompts(name, dtype, folders, models):
+    for i, n in enumerate([1, 2, 23, 97]):
+        seq = gc.prompt(30 + i, n, vocab(name))
+        r = gc.noisy_replay(folders[name], dtype, 128, models(name, dtype))
+        r.step([("r", seq, list(range(n)))], end=["r"])
+        gc.check_rows(r.rows, folders[name], {"r": seq}, dtype, f"whole {n}")
+
+
+def test_layer_outputs_equal_the_plain_layers(folders, models):
+    for name in NAMES:
+        seq = gc.prompt(3, 29, vocab(name))
+        config, w = gc.read_model(folders[name])
+        want = []
+        plain.forward(seq, w, config, layer_outputs=want)
+        r = gc.noisy_replay(folders[name], "float32", 64, models(name, "float32"), layer_outputs=True)
+        r.step([("r", seq[:20], [19])])
+        r.step([("r", seq[20:], [8])])
+        assert len(want) == len(models(name, "float32").spec.schedule)
+        for t in range(29):
+            got = r.layers[("r", t)]
+            for i in range(len(want)):
+                assert np.abs(got[i] - want[i][t]).max() <= 2e-4 * max(1.0, np.abs(want[i][t]).max()), (name, i, t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_prompt_then_token_by_token(name, dtype, folders, models):
+    n = 120
+    seq = gc.prompt(41, n, vocab(name))
+    r = gc.noisy_replay(folders[name], dtype, 128, models(name, dtype))
+    r.step([("r", seq[:n - 50], list(range(0, n - 50, 3)))])
+    for t in range(n - 50, n):
+        r.step([("r", [seq[t]], [0])])
+    gc.check_rows(r.rows, folders[name], {"r": seq}, dtype, "tail")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_every_token_decoded(name, dtype, folders, models):
+    """From the first token on, one by one (the first tokens of a sequence, then a long decode over many pages)."""
+    n = 70 if dtype == "bfloat16" else 260
+    seq = gc.prompt(42, n, vocab(name))
+    r = gc.noisy_replay(folders[name], dtype, 272, models(name, dtype))
+    for t in range(n):
+        r.step([("r", [seq[t]], [0] if t < 4 or t % 4 == 0 or t > n - 5 else [])])
+    gc.check_rows(r.rows, folders[name], {"r": seq}, dtype, "decoded")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_portions_down_to_two_tokens(name, dtype, folders, models):
+    portions = [7, 2, 16, 3, 2, 33, 1, 15, 2, 17, 2, 5, 1, 1, 2, 40]
+    n = sum(portions)
+    seq = gc.prompt(43, n, vocab(name))
+    r = gc.noisy_replay(folders[name], dtype, 160, models(name, dtype), page_size=8)
+    o = 0
+    for p in portions:
+        r.step([("r", seq[o:o + p], list(range(p)))])
+        o += p
+    gc.check_rows(r.rows, folders[name], {"r": seq}, dtype, "portions")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(name, dtype, folders, models):
+    """Five requests over three state slots and a pool of 14 pages of 16: portions of some beside single tokens of others;
+    a request that ends gives its pages and its slot (with the last token it saw) to the next, which must not see them."""
+    V = vocab(name)
+    seqs = {f"s{i}": gc.prompt(50 + i, n, V) for i, n in enumerate([61, 9, 130, 33, 47])}
+    r = gc.noisy_replay(folders[name], dtype, 14 * 16, models(name, dtype), max_requests=3)
+    at = {k: 0 for k in seqs}
+
+    def take(rid, n):
+        toks = seqs[rid][at[rid]:at[rid] + n]
+        want = [i for i in range(len(toks)) if (at[rid] + i) % 3 == 0 or at[rid] + i == len(seqs[rid]) - 1]
+        at[rid] += len(toks)
+        return (rid, toks, want)
+
+    def done(*rids):
+        return [x for x in rids if at[x] == len(seqs[x])]
+
+    r.step([take("s0", 20), take("s1", 2)])
+    r.step([take("s0", 1), take("s1", 1), take("s2", 50)])
+    r.step([take("s0", 40), take("s1", 6), take("s2", 1)], end=["s0", "s1"])
+    r.step([take("s2", 1), take("s3", 33)], end=["s3"])
+    r.step([take("s4", 2), take("s2", 30)])
+    while at["s2"] < 130 or at["s4"] < 47:
+        batch = [take(x, 1 if x == "s2" else 5) for x in ("s2", "s4") if at[x] < len(seqs[x])]
+        r.step(batch, end=done(*[b[0] for b in batch]))
+    assert all(at[k] == len(seqs[k]) for k in seqs)
+    gc.check_rows(r.rows, folders[name], seqs, dtype, "mixed")
+    assert len(r.cache.requests) == 0 and r.cache.available_pages() == [14] * len(r.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["G1", "G3"])
+def test_batched_rows_equal_the_rows_of_each_request_alone(name, dtype, folders, models):
+    """What a request's rows are does not depend on what else is in the batch, nor on pages and slots (float32: to the bit)."""
+    a, b = gc.prompt(60, 45, vocab(name)), gc.prompt(61, 18, vocab(name))
+    alone = gc.noisy_replay(folders[name], dtype, 128, models(name, dtype))
+    alone.step([("a", a[:30], list(range(30)))]); alone.step([("a", a[30:], list(range(15)))])
+    both = gc.noisy_replay(folders[name], dtype, 128, models(name, dtype))
+    both.step([("b", b[:10], [9]), ("a", a[:30], list(range(30)))])
+    both.step([("a", a[30:], list(range(15))), ("b", b[10:], [7])])
+    for p in range(45):
+        assert np.array_equal(alone.rows[("a", p)], both.rows[("a", p)]) or dtype == "bfloat16", p
+        assert np.abs(alone.rows[("a", p)] - both.rows[("a", p)]).max() <= (0 if dtype == "float32" else 0.05 * np.std(alone.rows[("a", p)]))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_few_wanted_rows_take_the_last_layers_shortcut(name, dtype, folders, models):
+    """Steps that want few rows (or none) run the last layer's attention, experts, token input and norms for those rows only
+    (G1: a last layer that caches its own rows; G2, G3: one that reads another layer's): the logits equal the plain
+    implementation's, the cache that later steps read is complete, and switching the shortcut off changes nothing beyond
+    rounding."""
+    n = 131
+    seq, other = gc.prompt(33, n, vocab(name)), gc.prompt(34, 40, vocab(name))
+    runs = {}
+    for shortcut in (True, False):
+        r = gc.noisy_replay(folders[name], dtype, 256, models(name, dtype))
+        r.runner.tail_shortcut = shortcut
+        r.step([("r", seq[:30], [])])
+        r.step([("r", seq[30:60], [29, 3]), ("o", other[:20], [19])])
+        r.step([("r", seq[60:n - 5], [0]), ("o", other[20:], [])])
+        r.step([("r", seq[n - 5:], list(range(5)))])
+        assert set(k for k in r.rows if k[0] == "r") == {("r", p) for p in [59, 33, 60] + list(range(n - 5, n))}
+        gc.check_rows(r.rows, folders[name], {"r": seq, "o": other}, dtype, f"shortcut {shortcut}")
+        runs[shortcut] = r.rows
+    assert models(name, dtype).layers[-1].supports_tail
+    for key, row in runs[True].items():
+        d = np.abs(row - runs[False][key]).max()
+        assert d <= (1e-4 if dtype == "float32" else 0.08 * np.std(row)), (key, d)
+
+
+def test_tensor_core_kernels_equal_the_float32_arithmetic_ones_in_a_model(folders, models):
+    """The same bfloat16 steps with the tensor-core attention and grouped products switched off: rows agree within rounding."""
+    from coheryn_ai_studio_b200 import ops
+    name = "G1"
+    seq = gc.prompt(62, 90, vocab(name))
+    rows = {}
+    for on in (True, False):
+        ops.set_maps_tc(on); ops.set_grouped_tc(on)
+        try:
+            r = gc.noisy_replay(folders[name], "bfloat16", 128, models(name, "bfloat16"))
+            r.step([("r", seq[:61], list(range(0, 61, 2)))])
+            for t in range(61, 90):
+                r.step([("r", [seq[t]], [0])])
+            rows[on] = r.rows
+        finally:
+            ops.set_maps_tc(True); ops.set_grouped_tc(True)
+    gc.check_rows(rows[False], folders[name], {"r": seq}, "bfloat16", "float32 arithmetic")
+    near = [np.abs(rows[True][k] - rows[False][k]).max() <= 0.05 * np.std(rows[False][k]) for k in rows[True]]
+    assert np.mean(near) > 0.9          # a router's near tie may fall the other way at single rows
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["G1", "G3"])
+def test_greedy_generation_through_the_engine(name, dtype, folders):
+    """The Python entry point with its scheduler, continuous batching, portions of 16 tokens and decode steps replayed
+    from CUDA graphs: every generated token is the plain implementation's first maximum given the tokens before it (in
+    bfloat16: or a near tie)."""
+    from coheryn_ai_studio_b200.engine import Engine
+    eng = Engine.from_folder(folders[name], dtype, context=128, max_num_seqs=3, max_num_batched_tokens=16, page_size=8)
+    prompts = [gc.prompt(70 + i, n, vocab(name)) for i, n in enumerate((3, 29, 50, 1))]
+    res = eng.generate(prompts, max_tokens=12)
+    for p, out in zip(prompts, res):
+        ids = list(p)
+        assert out.completion_tokens == 12 and out.finish_reason == "length"
+        for tok in out.token_ids:
+            ref = gc.plain_rows(folders[name], ids)[-1]
+            best = int(np.argmax(ref))
+            if tok != best:
+                gap = float(ref[best] - ref[tok]) / float(np.std(ref))
+                assert gap <= (1e-3 if dtype == "float32" else 0.4), (name, len(ids), tok, best, gap)
+            ids.append(tok)
+    eng.cache.check()
+    assert len(eng.cache.requests) == 0
+
+
+def test_trace_program_replays_a_schedule(folders, tmp_path):
+    """bin/trace_run on a folder of this design: portions, a second request, an ended request, a step that wants nothing."""
+    import json, os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "G2"
+    a, b = gc.prompt(80, 40, vocab(name)), gc.prompt(81, 12, vocab(name))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:25], "want": [0, 24]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[25:27], "want": []}, {"id": "b", "tokens": b, "want": [11]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[27:], "want": [12]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders[name], "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    V = vocab(name)
+    got0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(2, V)
+    got1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(1, V)
+    got2 = np.fromfile(out / "2.f32", dtype="<f4").reshape(1, V)
+    rows = {("a", 0): got0[0], ("a", 24): got0[1], ("b", 11): got1[0], ("a", 39): got2[0]}
+    gc.check_rows(rows, folders[name], {"a": a, "b": b}, "float32", "trace")
+
+
+def test_command_line_runs_and_inspects_the_design(folders):
+    import os, subprocess, sys
+    from coheryn_ai_studio_b200 import api
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "G1"
+    p = gc.prompt(85, 27, vocab(name))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "coheryn"), "run", folders[name], "--tokens", ",".join(map(str, p)),
+                        "--max-tokens", "5", "--context", "64", "--dtype", "float32", "--stream"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [int(t) for t in r.stdout.split()]
+    ids = list(p)
+    for tok in got:
+        assert tok == int(np.argmax(gc.plain_rows(folders[name], ids)[-1]))
+        ids.append(tok)
+    assert api.generate(folders[name], [p], max_tokens=5, context=64, dtype="float32")[0]["token_ids"] == got
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "coheryn"), "models", "inspect", folders[name]], capture_output=True,
+                       text=True, timeout=900)
+    assert r.returncode == 0 and "Guvusun" in r.stdout, r.stderr[-2000:]
+
+
+def test_zz_report():
+    print(f"\nGuvusun rows against the plain implementation: float32 largest |d| = {gc.WORST['float32']:.2e}; "
+          f"bfloat16 largest median distance = {gc.WORST['bfloat16']:.2f} of the bound")
