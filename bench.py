@@ -27,7 +27,9 @@ which no graph replays: it measures what such steps cost the host.  ``--workload
 (matrix-memory layers and attention beside a gated delta rule) at two layer sizes beside Qwen2 at equal sizes: prefill and
 decode through the step function, and the mixers' kernels alone.  ``--workload tutunex`` does the same for the Tutunex
 design (differential attention over chunks, attention with a sink beside a gated delta rule, norms before and after each
-sub-layer), its kernels beside the like kernels of the other models.
+sub-layer), its kernels beside the like kernels of the other models.  ``--workload guvusun`` does the same for the Guvusun
+design (latent attention with a learned sink and head gates, routed experts, norms after the sum) beside Qwen2 with a dense
+feed-forward of the experts' active size.
 """
 from __future__ import annotations
 
@@ -603,6 +605,182 @@ def tutunex_workload(args) -> int:
     return 0
 
 
+# Sizes of --workload guvusun.  Eight layers of latent attention with routed experts; layers 3 and 7 read the cached rows of
+# layers 2 and 6.  `small-latent`: cached rows of 256 channels (what the tensor-core attention is compiled for);
+# `wide-latent`: rows of 576 channels, the proportions of the large published models with latent attention.  Qwen2 beside
+# each at equal width, layers, head count, head size dim + rot_dim, two key/value heads (a cache of about the same bytes per
+# token) and a dense feed-forward of top x expert size (the same active matrix rows per token).
+GUVUSUN_SIZES = {
+    "small-latent": dict(width=2048, heads=16, dim=96, rot_dim=32, vdim=128, kv_rank=224, experts=30, identity=2, top=4,
+                         groups=(4, 2), ff=1024, side_dim=64, buckets=100003, vocab=32000, layers=8),
+    "wide-latent": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, experts=62, identity=2, top=6,
+                        groups=(8, 4), ff=1408, side_dim=64, buckets=100003, vocab=32000, layers=8),
+}
+
+
+def guvusun_config(z):
+    rot = {"dims": z["rot_dim"], "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    layers = []
+    for i in range(z["layers"]):
+        m = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+             "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "rot": rot}
+        if i % 4 == 3:
+            m["kv_from"] = i - 1
+        router = {"experts": z["experts"], "top": z["top"], "identity": z["identity"], "scale": 2.5,
+                  "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}
+        layers.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "moe", "expert": {"ff": z["ff"]}, "router": router}})
+    return {"architecture": "Guvusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "embedding": {"bigram": {"buckets": z["buckets"], "mul_prev": 127, "mul_cur": 7}}, "token_side": {"dim": z["side_dim"]},
+            "layers": layers}
+
+
+def guvusun_workload(args) -> int:
+    """Prefill and decode throughput of Guvusun and of Qwen2 at equal sizes through the step function, and the design's own
+    kernels alone beside the like kernels of Qwen2, each with its share of the roofline.  One JSON line."""
+    import numpy as np
+    import torch
+
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.config.guvusun import GuvusunConfig
+    from coheryn_ai_studio_b200.engine import random_model_on_device
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.position import ComputedRope, RotateHalfRope
+
+    tools = model_bench_tools(args)
+    pk, hbm, flops_peak, dev = tools.pk, tools.hbm, tools.flops_peak, tools.dev
+    tokens, batch, context = tools.tokens, tools.batch, tools.context
+    timed, step_like = tools.timed, tools.step_like
+
+    def kernels(z):
+        out = {}
+        H, dim, rd, dv, rank, page, W = z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["kv_rank"], args.page_size, z["width"]
+        row, hd = rank + rd, dim + rd
+        E, top, F, outputs = z["experts"], z["top"], z["ff"], z["experts"] + z["identity"]
+        f = lambda *shape: torch.randn(shape, device=dev)
+        b16 = lambda *shape: f(*shape).to(torch.bfloat16)
+        for name, lengths, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            B, T = len(lengths), sum(lengths)
+            per = -(-max(s + n for s, n in zip(starts, lengths)) // page)
+            tables = torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per)
+            st = step_like(lengths, starts, tables)
+            st.slots = [(tables[st.token_req.long(), (st.positions // page).long()] * page + st.positions % page).to(torch.int32)]
+            st.token_ids = torch.randint(0, z["vocab"], (T,), dtype=torch.int32, device=dev)
+            seen = sum(p + 1 for s, n in zip(starts, lengths) for p in range(s, s + n))
+            held = sum(s + n for s, n in zip(starts, lengths))
+
+            def attention(label, fn, issued_per_score, needed_per_score, cache_bytes, io_bytes):
+                ms = timed(fn)
+                out[f"{name}.{label}"] = {
+                    "ms": round(ms, 4), "tflops_issued": round(2.0 * H * issued_per_score * seen / ms / 1e9, 1),
+                    "of_bf16_peak_issued": round(2.0 * H * issued_per_score * seen / (ms / 1e3) / flops_peak, 4),
+                    "of_bf16_peak_needed": round(2.0 * H * needed_per_score * seen / (ms / 1e3) / flops_peak, 4),
+                    "of_hbm": round((cache_bytes + io_bytes) / (ms / 1e3) / hbm, 4)}
+            # the heads over ONE cached row per position whose first `rank` channels are also the values (queries carried
+            # into the latent space), and Qwen2's causal attention over two key/value heads at head size dim + rot_dim
+            kc = b16(B * per + 1, 1, page, row)
+            q, o = b16(T, H * row), torch.empty((T, H * rank), dtype=torch.bfloat16, device=dev)
+            sinks = f(H)
+            attention("latent_attention_sink", lambda: ops.attention_maps(
+                q, o, kc, None, st, 0, H, 1, row, rank, 1, page, None, None, True, hd ** -0.5, 0.0, False, 1e-6, 1.0,
+                sink_scores=sinks, values_in_keys=True), row + rank, min(row + rank, hd + dv), 2.0 * row * held, 2.0 * T * H * (row + rank))
+            G = 2
+            kq, vq = b16(B * per + 1, G, page, hd), b16(B * per + 1, G, page, hd)
+            qq, oq = b16(T, H * hd), torch.empty((T, H * hd), dtype=torch.bfloat16, device=dev)
+            attention("qwen2_attention_causal", lambda: ops.attention_rows(
+                qq, oq, kq, vq, tables, st.token_req, st.positions, H, G, hd, page, None, hd ** -0.5, cu_q=st.cu_q, kv_lens=st.kv_lens,
+                q_lens=st.q_lens, max_kv_len=st.max_kv_len), 2 * hd, 2 * hd, 4.0 * hd * G * held, 4.0 * T * H * hd)
+
+            def by_bytes(label, fn, by, flops=None):
+                ms = timed(fn)
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "of_hbm": round(by / (ms / 1e3) / hbm, 4)}
+                if flops is not None:
+                    out[f"{name}.{label}"].update({"tflops": round(flops / ms / 1e9, 1), "of_bf16_peak": round(flops / (ms / 1e3) / flops_peak, 4)})
+            # in front of the scores: latent normalised, both rotated parts turned by computed angles, the cache row written,
+            # the queries cast; Qwen2's rotation by table with its cache write
+            cols = H * hd + row + H
+            proj = f(T, cols)
+            wn = f(rank)
+            rope = ComputedRope(Runtime(torch.bfloat16, dev), rd, 10000.0, {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+            by_bytes("latent_prepare_and_cache_write", lambda: ops.latent_prepare(
+                proj, H, dim, rd, rank, H * hd, wn, 1e-6, st.positions, rope.frequency_pairs(), rd, rope.amplitude, st.slots[0], kc, page,
+                torch.bfloat16), T * (H * hd + row) * 4.0 + T * (H * dim + H * rd + row) * 2.0)
+            table = RotateHalfRope(Runtime(torch.bfloat16, dev), hd, hd, 1e6, context + tokens + 8).cos_sin()
+            qkv = b16(T, (H + 2 * G) * hd)
+            by_bytes("qwen2_rotate_by_table_and_cache_write",
+                     lambda: ops.rope_kv_write(qkv, st.positions, table, st.slots[0], kq, vq, H, G, hd, hd, page), 4.0 * T * (H + 2 * G) * hd)
+            # the products per head on both sides of the attention
+            qp, uk = b16(T, H * dim), b16(H, rank, dim)
+            by_bytes("queries_into_latent_space", lambda: ops.grouped_linear(qp, uk, q, a_col=dim, c_col=row),
+                     2.0 * (T * H * (dim + rank) + H * rank * dim), 2.0 * T * H * rank * dim)
+            uv, gates, og = b16(H, dv, rank), f(T, H), torch.empty((T, H * dv), dtype=torch.bfloat16, device=dev)
+            by_bytes("values_out_of_latent_space_gated", lambda: ops.grouped_linear(o, uv, og, a_col=rank, c_col=dv, factor=gates, factor_sigmoid=True),
+                     2.0 * (T * H * (dv + rank) + H * rank * dv), 2.0 * T * H * rank * dv)
+            # the stream: norm after the sum, and Qwen2's add with the next norm
+            x, d, w1 = f(T, W), f(T, W), f(W)
+            h = torch.empty((T, W), dtype=torch.bfloat16, device=dev)
+            by_bytes("scaled_add_then_norm", lambda: ops.scaled_add_norm(x, d, 2.0, w1, 1e-6, h), T * W * (4 + 4 + 4 + 2.0))
+            by_bytes("add_normalised_summand", lambda: ops.scaled_add_norm(x, d, 1.0, w1, 1e-6, h, normed_summand=True), T * W * (4 + 4 + 4 + 2.0))
+            resid, yb = f(T, W), b16(T, W)
+            by_bytes("qwen2_add_and_norm", lambda: ops.add_rmsnorm(resid, yb, w1, 1e-6, h), T * W * (2 + 8 + 2.0))
+            # the router and the experts, and a dense gated feed-forward of top x expert size
+            logits, corr = f(T, outputs), f(outputs) * 0.01
+            by_bytes("route_select", lambda: ops.route_select(logits, corr, z["groups"][0], z["groups"][1], top, 2.5), T * (outputs * 4.0 + top * 8.0))
+            ids, weights = ops.route_select(logits, corr, z["groups"][0], z["groups"][1], top, 2.5)
+            by_bytes("route_sort", lambda: ops.route_sort(ids, E), T * top * 12.0)
+            rows = ops.route_sort(ids, E)
+            real = int((ids < E).sum())
+            xb, wgu, wd = b16(T, W), b16(E, 2 * F, W), b16(E, W, F)
+            act, y = torch.empty((rows.n, F), dtype=torch.bfloat16, device=dev), torch.empty((rows.n, W), device=dev)
+            used = min(E, real)
+            by_bytes("experts_gate_up", lambda: ops.grouped_linear(xb, wgu, act, rows=rows, gather=True, epilogue=ops.gated_epilogue_word("silu", None)),
+                     2.0 * (used * 2 * F * W + real * (W + F)), 4.0 * real * F * W)
+            by_bytes("experts_down", lambda: ops.grouped_linear(act, wd, y, rows=rows), 2.0 * (used * F * W + real * F) + 4.0 * real * W,
+                     2.0 * real * F * W)
+            comb = torch.empty((T, W), device=dev)
+            by_bytes("route_combine", lambda: ops.route_combine(y, xb, ids, weights, rows, comb), 4.0 * real * W + T * W * 6.0)
+            Fd = top * F
+            wgu_d, wd_d = b16(2 * Fd, W), b16(W, Fd)
+            by_bytes("qwen2_dense_gate_up", lambda: ops.gated_linear(xb, wgu_d, "silu"), 2.0 * (2 * Fd * W + T * (W + Fd)), 4.0 * T * Fd * W)
+            actd = b16(T, Fd)
+            by_bytes("qwen2_dense_down", lambda: ops.linear(actd, wd_d, out_dtype=torch.float32), 2.0 * (Fd * W + T * Fd) + 4.0 * T * W, 2.0 * T * Fd * W)
+            # the token input of a layer: the gate's activation times the token's table columns
+            sd = z["side_dim"]
+            zt, tab, g = f(T, sd), b16(z["vocab"], z["layers"] * sd), torch.empty((T, sd), dtype=torch.bfloat16, device=dev)
+            by_bytes("token_table_gate", lambda: ops.gated_table_mul(zt, tab, sd, st.token_ids, g), T * sd * (4 + 2 + 2.0))
+        return out
+
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    results = {}
+    chosen = [n for n in GUVUSUN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in chosen:
+        z = GUVUSUN_SIZES[name]
+        entry = {}
+        model = random_model_on_device(GuvusunConfig.from_dict(guvusun_config(z)), seed=0, dtype="bfloat16", device="cuda:0")
+        entry["guvusun"] = tools.run_model(model, z["vocab"])
+        del model
+        torch.cuda.empty_cache()
+        qcfg = Qwen2Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["top"] * z["ff"],
+                           num_hidden_layers=z["layers"], num_attention_heads=z["heads"], num_key_value_heads=2,
+                           head_dim=z["dim"] + z["rot_dim"], max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6,
+                           tie_word_embeddings=False)
+        model = random_model_on_device(qcfg, seed=0, dtype="bfloat16", device="cuda:0")
+        entry["qwen2_equal_size"] = tools.run_model(model, z["vocab"])
+        del model
+        torch.cuda.empty_cache()
+        if not args.no_kernels:
+            entry["kernels"] = kernels(z)
+        results[name] = entry
+    clocks = ClockSampler.summary(sampler.window(t0, time.time()))
+    sampler.stop()
+    print(json.dumps({"workload": "guvusun", "dtype": "bf16", "data": "synthetic", "prefill_tokens": tokens, "decode_batch": batch,
+                      "decode_context": context, "decode_steps": tools.steps, "peaks": pk, "clocks": clocks,
+                      "l2": "flushed before each timed kernel", "gpu_launches": ops.total_launch_count(), "sizes": results}))
+    return 0
+
+
 def timeline(args, make_engine, StepEntry, ops, torch) -> int:
     """Where a decode step's time goes, kernel by kernel, measured inside graph-replayed steps (the
     kernels overlap through programmatic dependent launch, so a kernel's own duration says little):
@@ -670,9 +848,10 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b", "kapudra", "tutunex"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b", "kapudra", "tutunex", "guvusun"],
                     help="decode: the contract's line (default); the others: see the header")
-    ap.add_argument("--sizes", default="", help="--workload kapudra / tutunex: which of its sizes (comma separated; default all)")
+    ap.add_argument("--sizes", default="", help="--workload kapudra / tutunex / guvusun: which of its sizes (comma separated; default all)")
+    ap.add_argument("--no-kernels", action="store_true", help="--workload guvusun: the models only, not the kernels alone")
     ap.add_argument("--timeline-raw", action="store_true", help="with --timeline: also every kernel's start and end")
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the benchmark: the kernels of one graph-replayed decode step with their times "
@@ -693,6 +872,8 @@ def main() -> int:
         return kapudra_workload(args)
     if args.workload == "tutunex":
         return tutunex_workload(args)
+    if args.workload == "guvusun":
+        return guvusun_workload(args)
     if args.workload != "decode":
         return other_workload(args)
 

@@ -29,7 +29,7 @@
 namespace {
 
 constexpr int DK = CO_MAPS_DK, DV = CO_MAPS_DV, MAPS = CO_MAPS_N;
-static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 256 && DV <= 256, "head sizes: multiples of 16 up to 256");
+static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 1024 && DV <= 1024, "head sizes: multiples of 16 up to 1024");
 static_assert(MAPS == 1 || MAPS == 2, "one score map or two");
 constexpr int KROW = MAPS * DK;                  // channels of a key row (and of a query head)
 #ifdef CO_MAPS_V_IN_K
@@ -40,6 +40,7 @@ constexpr bool V_IN_K = false;
 #endif
 constexpr int KS = KROW + 8;                     // padded row strides in shared memory: an odd number of 16-byte units
 constexpr int VS = V_IN_K ? KS : DV + 8;
+constexpr int VROW = V_IN_K ? 0 : VS;            // shared-memory elements of a value row (none when it is the key row)
 constexpr int BM = 64, WARPS = 4;
 #ifdef CO_MAPS_BN
 constexpr int BN = CO_MAPS_BN;                   // a measuring switch: keys per tile
@@ -47,7 +48,17 @@ constexpr int BN = CO_MAPS_BN;                   // a measuring switch: keys per
 constexpr int BN = 32;      // measured on a B200: tiles of 32 keys with three resident CTAs per SM beat tiles of 64 with two by 12 %
 #endif
 static_assert(BN == 32 || BN == 64, "key tiles of 32 or 64 positions");
-constexpr int NT = BN / 8, OT = DV / 8;
+// A warp's accumulator holds at most 256 value channels.  Wider values are taken in equal CHUNKS of DVC channels, one
+// after the other: the pass over the keys that multiplies weights and values runs once per chunk and computes the scores
+// again (the same instructions, hence the same bits), so every chunk sees the same weights.
+constexpr int value_chunk(int dv) {
+  if (dv <= 256) return dv;
+  for (int c = 256; c > 16; c -= 16)
+    if (dv % c == 0) return c;
+  return 16;
+}
+constexpr int DVC = value_chunk(DV), NCH = DV / DVC;
+constexpr int NT = BN / 8, OT = DVC / 8;
 constexpr int MAX_SPLITS = 16;
 typedef __nv_bfloat16 bf16;
 
@@ -214,7 +225,7 @@ __global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kerne
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);        // [BM][KS]
   bf16* ks = qs + BM * KS;                             // [2][BN][KS]
   bf16* vs = ks + 2 * BN * KS;                         // [2][BN][VS]
-  int* tbl = reinterpret_cast<int*>(vs + 2 * BN * VS); // [table_cache]
+  int* tbl = reinterpret_cast<int*>(vs + 2 * BN * VROW); // [table_cache]
   co_pdl_launch_dependents();
   co_pdl_wait();
   const int r = blockIdx.y, h = blockIdx.z;
@@ -310,7 +321,9 @@ __global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kerne
       mx[m][rr] = M;
     }
 
-  // pass 2: the weights, and their product with the values
+  // pass 2: the weights, and their product with the values (once per chunk of value channels)
+  for (int vc = 0; vc < NCH; ++vc) {
+  if (vc) __syncthreads();                       // the last tile of the chunk before is read no more
   float o[OT][4];
 #pragma unroll
   for (int nt = 0; nt < OT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
@@ -347,7 +360,7 @@ __global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kerne
           for (int e = 0; e < 4; ++e) w[nt][e] -= A.lambda * (ex2(s[nt][e] - mx[MAPS - 1][e >> 1]) * inv[MAPS - 1][e >> 1]);
       }
     }
-    weights_times_values(o, w, V_IN_K ? kt : vs + (i & 1) * BN * VS, lane);
+    weights_times_values(o, w, (V_IN_K ? kt : vs + (i & 1) * BN * VS) + vc * DVC, lane);
     }
     __syncthreads();
   }
@@ -355,18 +368,19 @@ __global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kerne
   for (int rr = 0; rr < 2; ++rr) {
     const int row = warp * 16 + (lane >> 2) + 8 * rr;
     float factor = A.out_scale;
-    if (A.head_norm) {
+    if (A.head_norm) {                           // (the launcher refuses it for values in several chunks)
       float ss = 0.f;
 #pragma unroll
       for (int nt = 0; nt < OT; ++nt) ss += o[nt][2 * rr] * o[nt][2 * rr] + o[nt][2 * rr + 1] * o[nt][2 * rr + 1];
       factor *= 1.0f / sqrtf(quad_sum(ss) / (float)DV + A.eps);
     }
     if (row < rows) {
-      bf16* orow = A.out + (size_t)(q0 + tile * BM + row) * A.ldo + (size_t)h * DV + 2 * (lane & 3);
+      bf16* orow = A.out + (size_t)(q0 + tile * BM + row) * A.ldo + (size_t)h * DV + vc * DVC + 2 * (lane & 3);
 #pragma unroll
       for (int nt = 0; nt < OT; ++nt)
         *reinterpret_cast<__nv_bfloat162*>(orow + nt * 8) = __floats2bfloat162_rn(o[nt][2 * rr] * factor, o[nt][2 * rr + 1] * factor);
     }
+  }
   }
 }
 
@@ -397,7 +411,7 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
   }
   cp_commit();
   bf16* kw = kall + warp * BN * KS;
-  bf16* vw = vall + warp * BN * VS;
+  bf16* vw = vall + warp * BN * VROW;
   const int quarter = split_keys / WARPS;                         // a multiple of BN
   const int w_lo = key_lo + warp * quarter, w_hi = min(w_lo + quarter, p + 1);
   const int pos[2] = {(lane >> 2) < group ? p : -1, (lane >> 2) + 8 < group ? p : -1};
@@ -406,13 +420,14 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
   cp_commit();
   cp_wait<0>();
   __syncthreads();
-  for (int m = 0; m < MAPS; ++m) {
+  for (int pass = 0; pass < MAPS * NCH; ++pass) {      // a map's chunks of value channels one after the other
+    const int m = pass / NCH, vc = pass % NCH;
     float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
     float o[OT][4];
 #pragma unroll
     for (int nt = 0; nt < OT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
     for (int key0 = w_lo; key0 < w_hi; key0 += BN) {
-      if (key0 != w_lo || (m > 0 && w_lo + BN < w_hi)) {       // the first tile is there already, unless a later one took its place
+      if (key0 != w_lo || (pass > 0 && w_lo + BN < w_hi)) {       // the first tile is there already, unless a later one took its place
         __syncwarp();
         load_keys<32>(kw, vw, A, table, kvh, key0, p + 1, lane);
         cp_commit();
@@ -443,7 +458,7 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
 #pragma unroll
         for (int nt = 0; nt < OT; ++nt) { o[nt][2 * rr] *= corr; o[nt][2 * rr + 1] *= corr; }
       }
-      weights_times_values(o, s, V_IN_K ? kw : vw, lane);
+      weights_times_values(o, s, (V_IN_K ? kw : vw) + vc * DVC, lane);
     }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -453,8 +468,8 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
         float* part = scratch + ((((size_t)r * A.nh + kvh * group + row) * MAPS + m) * (n_splits * WARPS) + split * WARPS + warp) * (DV + 2);
 #pragma unroll
         for (int nt = 0; nt < OT; ++nt) {
-          part[nt * 8 + 2 * (lane & 3)] = o[nt][2 * rr];
-          part[nt * 8 + 2 * (lane & 3) + 1] = o[nt][2 * rr + 1];
+          part[vc * DVC + nt * 8 + 2 * (lane & 3)] = o[nt][2 * rr];
+          part[vc * DVC + nt * 8 + 2 * (lane & 3) + 1] = o[nt][2 * rr + 1];
         }
         if ((lane & 3) == 0) { part[DV] = mx[rr]; part[DV + 1] = l; }
       }
@@ -567,6 +582,7 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
   if (nkv <= 0 || nh % nkv) CO_FAIL("attention_maps_bf16: %d heads do not group over %d kv heads", nh, nkv);
   if ((ldq & 7) || (ldo & 1) || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
     CO_FAIL("attention_maps_bf16: rows of q must start on 16-byte boundaries, rows of out on 4-byte ones");
+  if (head_norm && NCH > 1) CO_FAIL("attention_maps_bf16: a normalised output needs values of at most 256 channels (%d)", DV);
   const int group = nh / nkv;
   const bool decode = any_single && group <= 16;
   MapsArgs A{(const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q,
@@ -578,7 +594,7 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
     if (window > 0 && window < visible) visible = window;
     const long entries = ((long)visible + BM + 2 * BN) / page_size + 2;
     A.table_cache = entries <= 4096 ? (int)entries : 0;    // a longer table is read from global memory
-    const size_t smem = ((size_t)BM * KS + (size_t)2 * BN * KS + (size_t)2 * BN * VS) * sizeof(bf16) + (size_t)A.table_cache * sizeof(int);
+    const size_t smem = ((size_t)BM * KS + (size_t)2 * BN * KS + (size_t)2 * BN * VROW) * sizeof(bf16) + (size_t)A.table_cache * sizeof(int);
     if (smem > 48 * 1024) cudaFuncSetAttribute(maps_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     co_launch(maps_tiles_kernel, dim3((max_q_len + BM - 1) / BM, B, nh), dim3(WARPS * 32), smem, stream, A);
     CO_CHECK_LAUNCH("maps_tiles");
@@ -588,7 +604,7 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
       CO_FAIL("attention_maps_bf16: scratch of %ld floats is too small", scratch_floats);
     int split_keys, n_splits;
     decode_plan(max_kv_len, window, chunk, &split_keys, &n_splits);
-    const size_t smem = ((size_t)16 * KS + (size_t)WARPS * BN * (KS + VS)) * sizeof(bf16);
+    const size_t smem = ((size_t)16 * KS + (size_t)WARPS * BN * (KS + VROW)) * sizeof(bf16);
     if (smem > 48 * 1024) cudaFuncSetAttribute(maps_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     co_launch(maps_decode_kernel, dim3(B, nkv, n_splits), dim3(WARPS * 32), smem, stream, A, scratch, split_keys, n_splits);
     CO_CHECK_LAUNCH("maps_decode");

@@ -258,8 +258,8 @@ def routed_library() -> ctypes.CDLL:
 def maps_attention_library(dk: int, dv: int, maps: int, values_in_keys: bool = False) -> ctypes.CDLL:
     """The tensor-core kernels of the attention with score maps, compiled for one (channels per map, value channels,
     maps) when a model needs them; ``values_in_keys``: the values are the first ``dv`` channels of the key rows."""
-    if dk % 16 or dv % 16 or not 16 <= dk <= 256 or not 16 <= dv <= 256 or maps not in (1, 2):
-        raise BuildError(f"the tensor-core attention with score maps takes head sizes 16..256 in steps of 16 and one or "
+    if dk % 16 or dv % 16 or not 16 <= dk <= 1024 or not 16 <= dv <= 1024 or maps not in (1, 2):
+        raise BuildError(f"the tensor-core attention with score maps takes head sizes 16..1024 in steps of 16 and one or "
                          f"two maps, not ({dk}, {dv}, {maps})")
     defines = {"CO_MAPS_DK": dk, "CO_MAPS_DV": dv, "CO_MAPS_N": maps}
     if os.environ.get("COHERYN_MAPS_BN"):       # a measuring switch: keys per tile (32 or 64)

@@ -1202,8 +1202,12 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * maps * dk and out.shape == (T, num_heads * dv)
     assert k_cache.dtype == q.dtype and out.dtype == q.dtype and v_cache.dtype == q.dtype
     q_lens = getattr(step, "q_lens", None)
-    fast = (MAPS_TC and not force_simple and q.dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and 16 <= dk <= 256
-            and 16 <= dv <= 256 and q_lens and getattr(step, "max_kv_len", None) and getattr(step, "cu_q", None) is not None
+    # what the tensor-core kernels keep in shared memory: 64 query rows, two tiles of 32 key rows (and of value rows when
+    # those are rows of their own), up to 4,096 block-table entries; values wider than 256 channels go in chunks
+    tc_smem = 2 * (128 * (maps * dk + 8) + (0 if values_in_keys else 64 * (dv + 8))) + 16384
+    fast = (MAPS_TC and not force_simple and q.dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and 16 <= dk <= 1024
+            and 16 <= dv <= 1024 and tc_smem <= 227 * 1024 and not (head_norm and dv > 256)
+            and q_lens and getattr(step, "max_kv_len", None) and getattr(step, "cu_q", None) is not None
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)
     if fast:
         # rows that are whole runs of consecutive positions per request, ending at the request's last position

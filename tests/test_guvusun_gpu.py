@@ -266,6 +266,7 @@ MIXERS = [
     (shape(3, 12, 6, 10, 20, {"dims": 6, "base": 77.0}), 100, 16),              # nothing divides: the float32-arithmetic kernels
     (shape(2, 40, 32, 24, 224, {"dims": 32, "base": 50.0}), 80, 16),            # rows of 256 channels
     (shape(1, 8, 4, 8, 300, {"dims": 4, "base": 9.0}), 64, 4),                  # a latent wider than any tile
+    (shape(2, 16, 16, 16, 320, YARN), 64, 16),                                  # wider than an accumulator: values in two chunks
 ]
 
 
@@ -303,7 +304,7 @@ def test_latent_attention_in_portions_and_decoded(dtype, m, width, page):
 
 
 @pytest.mark.parametrize("tensor_cores", [True, False])
-@pytest.mark.parametrize("m,width,page", [MIXERS[0], MIXERS[1], (shape(2, 24, 32, 16, 64, {"dims": 32, "base": 10000.0}), 64, 8)])
+@pytest.mark.parametrize("m,width,page", [MIXERS[0], MIXERS[1], MIXERS[5], (shape(2, 24, 32, 16, 64, {"dims": 32, "base": 10000.0}), 64, 8)])
 def test_one_key_that_stands_out_far_back_and_at_the_borders(tensor_cores, m, width, page):
     """The slowest-turning pair of the rotated key part of ONE position and of every query carries a large component, so a
     row that may see that position puts nearly all its weight there: at position 0, on both sides of page and tile borders,
