@@ -737,6 +737,14 @@ def guvusun_workload(args) -> int:
                      2.0 * (used * 2 * F * W + real * (W + F)), 4.0 * real * F * W)
             by_bytes("experts_down", lambda: ops.grouped_linear(act, wd, y, rows=rows), 2.0 * (used * F * W + real * F) + 4.0 * real * W,
                      2.0 * real * F * W)
+            if ops.grouped_tc_suits(xb, T * top, E, wgu, wd):      # many rows per expert: the TMA + tcgen05 kernel over 128-row tiles
+                wide = ops.route_sort(ids, E, wide_tiles=True)
+                by_bytes("experts_rows_in_sorted_order", lambda: ops.gather_rows(xb, wide.token_of), 4.0 * wide.n * W)
+                xs = ops.gather_rows(xb, wide.token_of)
+                by_bytes("experts_gate_up_tcgen05", lambda: ops.gemm_bf16_tc_grouped(xs, wgu, act, wide, ops.gated_epilogue_word("silu", None)),
+                         2.0 * (used * 2 * F * W + real * (W + F)), 4.0 * real * F * W)
+                by_bytes("experts_down_tcgen05", lambda: ops.gemm_bf16_tc_grouped(act, wd, y, wide), 2.0 * (used * F * W + real * F) + 4.0 * real * W,
+                         2.0 * real * F * W)
             comb = torch.empty((T, W), device=dev)
             by_bytes("route_combine", lambda: ops.route_combine(y, xb, ids, weights, rows, comb), 4.0 * real * W + T * W * 6.0)
             Fd = top * F

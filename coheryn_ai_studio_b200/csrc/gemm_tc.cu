@@ -81,12 +81,21 @@ __device__ __forceinline__ void store_chunk_tma(unsigned tmem_chunk, const float
 }
 constexpr int STAGING_BYTES = 4 * 2 * 4096;   // four epilogue warps, two chunks each
 
+// Row tiles that each meet a matrix of their own (the rows of x are ordered by group, W holds the groups' matrices one
+// below the other, `w_rows` rows each): tile y of the grid is rows row0[y] .. of group group[y], which end at
+// offsets[group + 1]; tiles from n_tiles[0] on do not exist.  All on the device, written by an earlier kernel.
+struct GroupTiles {
+  const int* group; const int* row0; const int* offsets; const int* n_tiles;
+  int w_rows;
+};
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, int tma_out,
                const void* __restrict__ bias, int bias_dtype, void* __restrict__ out, int out_dtype, int M, int N,
-               int K, long ldo, int epilogue, int* __restrict__ status, float* __restrict__ partial, int k_per_split) {
+               int K, long ldo, int epilogue, int* __restrict__ status, float* __restrict__ partial, int k_per_split,
+               GroupTiles gt) {
   using S = Smem<BN, STAGES>;
   extern __shared__ unsigned char smem_raw[];
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
@@ -98,7 +107,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   float* bias_s = (float*)(tiles + STAGES * S::STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  int m0 = blockIdx.y * BM, wn0 = blockIdx.x * BN;       // first row of x and of W
+  const int n0 = blockIdx.x * BN;
+  if (gt.group) {             // grouped: the tile list comes from the kernel before
+    co_pdl_wait();
+    if ((int)blockIdx.y >= gt.n_tiles[0]) return;         // the whole CTA, before anything is set up
+    const int g = gt.group[blockIdx.y];
+    m0 = gt.row0[blockIdx.y];
+    M = min(M, gt.offsets[g + 1]);                        // rows of the next group in the tile are computed and not stored
+    wn0 = g * gt.w_rows + n0;
+  }
   // Split K: CTA z of the grid sums the k-steps [kt_begin, kt_begin + k_tiles) and leaves its raw
   // float32 tile in partial[z]; splitk_reduce_kernel adds the splits in order and finishes.
   const int kt_begin = partial ? blockIdx.z * k_per_split : 0;
@@ -126,7 +144,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int head = k_tiles < STAGES ? k_tiles : STAGES;
       for (int kt = 0; kt < head; ++kt) {
         mbar_expect_tx(&full[kt], S::STAGE_BYTES);
-        tma_load_2d(tiles + kt * S::STAGE_BYTES + S::A_BYTES, &map_w, (kt_begin + kt) * BK, n0, &full[kt]);
+        tma_load_2d(tiles + kt * S::STAGE_BYTES + S::A_BYTES, &map_w, (kt_begin + kt) * BK, wn0, &full[kt]);
       }
       co_pdl_wait();
       for (int kt = 0; kt < head; ++kt)
@@ -137,7 +155,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         unsigned char* a = tiles + s * S::STAGE_BYTES;
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
         tma_load_2d(a, &map_x, (kt_begin + kt) * BK, m0, &full[s]);
-        tma_load_2d(a + S::A_BYTES, &map_w, (kt_begin + kt) * BK, n0, &full[s]);
+        tma_load_2d(a + S::A_BYTES, &map_w, (kt_begin + kt) * BK, wn0, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -758,7 +776,7 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
   const int used = partial ? (k_tiles + k_per_split - 1) / k_per_split : 1;    // no split is left empty
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, used);
   cudaError_t le = co_launch(kernel, grid, dim3(192), (size_t)smem, stream, mx, mw, mo, tma_out, bias, bias_dtype, out, out_dtype, M, N,
-                             K, ldo, epilogue, status, used > 1 ? partial : (float*)nullptr, k_per_split);
+                             K, ldo, epilogue, status, used > 1 ? partial : (float*)nullptr, k_per_split, GroupTiles{});
   if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
   CO_CHECK_LAUNCH("gemm_tc");
   if (used > 1 && !leave_parts) {
@@ -769,6 +787,21 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
     if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
     CO_CHECK_LAUNCH("splitk_reduce");
   }
+  return 0;
+}
+// The same kernel over row tiles of groups (see GroupTiles): the grid's second dimension is an upper bound of the tiles.
+template <int BN, int STAGES>
+int launch_tc_grouped(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int out_dtype, int M, int N, int K, long ldo,
+                      int epilogue, int* status, const GroupTiles& gt, int max_tiles, cudaStream_t stream) {
+  auto kernel = gemm_tc_kernel<BN, STAGES>;
+  constexpr int smem = Smem<BN, STAGES>::TOTAL;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) CO_FAIL("gemm_tc: %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  dim3 grid((N + BN - 1) / BN, max_tiles, 1);
+  cudaError_t le = co_launch(kernel, grid, dim3(192), (size_t)smem, stream, mx, mw, mx, 0, (const void*)nullptr, 0, out, out_dtype, M, N,
+                             K, ldo, epilogue, status, (float*)nullptr, (K + BK - 1) / BK, gt);
+  if (le != cudaSuccess) CO_FAIL("gemm_tc: launch failed: %s", cudaGetErrorString(le));
+  CO_CHECK_LAUNCH("gemm_tc_grouped");
   return 0;
 }
 template <int BN, int STAGES>
@@ -942,6 +975,32 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (bn == 64) GO(64, 8);
   GO(32, 8);
 #undef GO
+}
+
+// Rows per tile of the grouped product below.
+CO_EXPORT int coheryn_gemm_tc_grouped_tile_rows() { return BM; }
+
+// out[rows of group g] = x[rows of group g] . W_g^T for rows ordered by group: x [M, K] bfloat16 (row stride ldx), w [G, N, K]
+// bfloat16 contiguous, out [M, N] (or [M, N / 2] behind a gated epilogue) bfloat16 or float32; tile lists of 128-row tiles
+// as GroupTiles describes them, `max_tiles` an upper bound of their number.  Rows that belong to no tile are not written.
+CO_EXPORT int coheryn_gemm_bf16_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int G,
+                                           long ldx, long ldo, int epilogue, const int* tile_group, const int* tile_row0,
+                                           const int* offsets, const int* n_tiles, int max_tiles, int* status,
+                                           cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || G <= 0 || max_tiles <= 0) return 0;
+  if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc_grouped: K = %d and the row stride %ld must be multiples of 8", K, ldx);
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc_grouped: operands must be 16-byte aligned");
+  if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_tc_grouped: gated epilogue needs an even number of rows");
+  if (!co_epilogue_known(epilogue)) CO_FAIL("gemm_bf16_tc_grouped: unknown epilogue %d", epilogue);
+  if (!tile_group || !tile_row0 || !offsets || !n_tiles || !status) CO_FAIL("gemm_bf16_tc_grouped: the tile lists are missing");
+  const int bn = N >= 192 ? 256 : (N >= 96 ? 128 : 64);
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, (long)G * N, K, K, bn))
+    CO_FAIL("gemm_bf16_tc_grouped: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d G=%d ldx=%ld)", M, N, K, G, ldx);
+  const GroupTiles gt{tile_group, tile_row0, offsets, n_tiles, N};
+  if (bn == 256) return launch_tc_grouped<256, 4>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
+  if (bn == 128) return launch_tc_grouped<128, 6>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
+  return launch_tc_grouped<64, 8>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
 }
 
 // How many K slices coheryn_gemm_bf16_tc_parts leaves for this shape (0 or 1: the shape is not split,

@@ -410,15 +410,17 @@ CO_EXPORT int coheryn_route_select(const float* logits, long ld, const void* cor
 // Rows per tile of the grouped products, by the kernel that will run (both use the same today).
 CO_EXPORT int coheryn_grouped_tile_rows() { return TBM; }
 
+// tile_rows: the rows per tile of the product that will read the lists (0: those of the grouped kernels of this file).
 CO_EXPORT int coheryn_route_sort(const int* ids, int n, int top, int E, int* offsets, int* row_of, int* token_of, int* tile_group,
-                                 int* tile_row0, int* n_tiles, cudaStream_t stream) {
+                                 int* tile_row0, int* n_tiles, int tile_rows, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (E < 1 || top < 1) CO_FAIL("route_sort: bad sizes");
+  if (E < 1 || top < 1 || tile_rows < 0) CO_FAIL("route_sort: bad sizes");
+  if (tile_rows == 0) tile_rows = TBM;
   static_assert(TBM == SBM, "both grouped kernels take the same row tiles");
   const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
   if (smem > 200 * 1024) CO_FAIL("route_sort: %d experts do not fit in shared memory", E);
   if (smem > 48 * 1024) cudaFuncSetAttribute(route_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  co_launch(route_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, n, top, E, TBM, offsets, row_of, token_of, tile_group,
+  co_launch(route_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, n, top, E, tile_rows, offsets, row_of, token_of, tile_group,
             tile_row0, n_tiles);
   CO_CHECK_LAUNCH("route_sort");
   return 0;

@@ -1352,20 +1352,22 @@ def route_select(logits: torch.Tensor, correction: Optional[torch.Tensor], n_gro
 
 class RoutedRows:
     """The (token, choice) pairs of a step ordered by expert, as ``route_sort`` leaves them on the device."""
-    __slots__ = ("n", "experts", "offsets", "row_of", "token_of", "tile_group", "tile_row0", "n_tiles", "max_tiles")
+    __slots__ = ("n", "experts", "offsets", "row_of", "token_of", "tile_group", "tile_row0", "n_tiles", "max_tiles", "tile_rows")
 
 
-def route_sort(ids: torch.Tensor, experts: int) -> RoutedRows:
-    """Order the pairs whose id names one of the first ``experts`` outputs by expert."""
+def route_sort(ids: torch.Tensor, experts: int, wide_tiles: bool = False) -> RoutedRows:
+    """Order the pairs whose id names one of the first ``experts`` outputs by expert.  ``wide_tiles``: row tiles for
+    ``gemm_bf16_tc_grouped`` instead of ``grouped_linear``; every index of the book is then a valid one (rows that no pair
+    takes name token 0)."""
     _dev(ids)
     _i32(ids, "ids")
     T, top = ids.shape
     n = T * top
     lib = routed()
-    bm = int(lib.coheryn_grouped_tile_rows())
+    bm = int(core().coheryn_gemm_tc_grouped_tile_rows()) if wide_tiles else int(lib.coheryn_grouped_tile_rows())
     r = RoutedRows()
-    r.n, r.experts, r.max_tiles = n, experts, n // bm + experts
-    book = torch.empty(experts + 1 + 2 * n + 2 * r.max_tiles + 1, dtype=torch.int32, device=ids.device)
+    r.n, r.experts, r.max_tiles, r.tile_rows = n, experts, n // bm + experts, bm
+    book = (torch.zeros if wide_tiles else torch.empty)(experts + 1 + 2 * n + 2 * r.max_tiles + 1, dtype=torch.int32, device=ids.device)
     o = 0
     r.offsets = book[o:o + experts + 1]; o += experts + 1
     r.row_of = book[o:o + n]; o += n
@@ -1374,8 +1376,37 @@ def route_sort(ids: torch.Tensor, experts: int) -> RoutedRows:
     r.tile_row0 = book[o:o + r.max_tiles]; o += r.max_tiles
     r.n_tiles = book[o:o + 1]
     _check(lib, lib.coheryn_route_sort(_ptr(ids), c_int(n), c_int(top), c_int(experts), _ptr(r.offsets), _ptr(r.row_of),
-                                       _ptr(r.token_of), _ptr(r.tile_group), _ptr(r.tile_row0), _ptr(r.n_tiles), _stream()))
+                                       _ptr(r.token_of), _ptr(r.tile_group), _ptr(r.tile_row0), _ptr(r.n_tiles),
+                                       c_int(bm if wide_tiles else 0), _stream()))
     return r
+
+
+# Pairs per expert (on average) from which the routed products take the TMA + tcgen05 kernel: its row tiles are 128 rows.
+GROUPED_TC_MIN_ROWS = int(os.environ.get("COHERYN_GROUPED_TC_MIN_ROWS", "48"))
+
+
+def grouped_tc_suits(x: torch.Tensor, pairs: int, experts: int, *weights: torch.Tensor) -> bool:
+    """Whether the routed products of ``pairs`` (token, choice) pairs over ``experts`` matrices run on the TMA + tcgen05
+    kernel: bfloat16, inner sizes in multiples of 8, and rows enough to fill its tiles."""
+    return (GROUPED_TC and x.dtype == torch.bfloat16 and pairs >= GROUPED_TC_MIN_ROWS * experts
+            and all(w.dtype == torch.bfloat16 and w.shape[2] % 8 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0
+                    for w in weights))
+
+
+def gemm_bf16_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: RoutedRows, epilogue: int = 0) -> None:
+    """out[r] = a[r] . w[expert of sorted row r]^T for the rows of ``route_sort(..., wide_tiles=True)``, on the TMA +
+    tcgen05 kernel of ``csrc/gemm_tc.cu``; ``a`` [pairs, K] bfloat16 in sorted order, ``w`` [G, N, K]; ``epilogue``: a gated
+    epilogue word (``out`` then has N / 2 columns).  Rows beyond the last expert's are not written."""
+    _dev(a, w, out)
+    G, N, K = w.shape
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and a.shape == (rows.n, K)
+    assert a.stride(1) == 1 and out.stride(1) == 1 and out.shape == (rows.n, N // 2 if epilogue else N) and G == rows.experts
+    lib = core()
+    assert rows.tile_rows == int(lib.coheryn_gemm_tc_grouped_tile_rows())
+    _check(lib, lib.coheryn_gemm_bf16_tc_grouped(
+        _ptr(a), _ptr(w), _ptr(out), c_int(_code(out)), c_int(rows.n), c_int(N), c_int(K), c_int(G), c_long(a.stride(0)),
+        c_long(out.stride(0)), c_int(int(epilogue)), _ptr(rows.tile_group), _ptr(rows.tile_row0), _ptr(rows.offsets),
+        _ptr(rows.n_tiles), c_int(rows.max_tiles), _ptr(tc_status(a.device)), _stream()))
 
 
 def grouped_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: Optional[RoutedRows] = None,

@@ -10,7 +10,9 @@ the ``top`` largest choice scores are chosen, ties to the lower index.  The weig
 their sum (+ 1e-20) times ``scale``; the result is the weighted sum of the chosen experts' outputs.
 
 The pairs (token, choice) that name a real expert are ordered by expert on the device, each expert's rows meet its
-matrices in one grouped product (gate and up interleaved, the activation in the epilogue; then down), and a last kernel
+matrices in one grouped product (gate and up interleaved, the activation in the epilogue; then down; with many rows per
+expert the products are the TMA + tcgen05 kernel of the dense layers over row tiles of 128, with fewer the kernel of
+``csrc/routed.cu`` over tiles of 64, which reads the tokens' rows through the index), and a last kernel
 adds a token's weighted rows in the order of its choices, so a token's result does not depend on the other tokens of the
 step.  Nothing is read back to the host: the part can be captured in a CUDA graph.
 
@@ -85,12 +87,17 @@ class RoutedExperts(FeedForward):
         if T == 0:
             return out
         ids, weights = self.choose(x)
-        rows = ops.route_sort(ids, self.experts)
+        wide = ops.grouped_tc_suits(x, T * self.top, self.experts, self.w_gate_up, self.w_down)
+        rows = ops.route_sort(ids, self.experts, wide_tiles=wide)
         n = rows.n
         y = torch.empty((n, self.hidden_size), dtype=torch.float32, device=x.device)
         act = torch.empty((n, self.expert_size), dtype=x.dtype, device=x.device)
-        ops.grouped_linear(x, self.w_gate_up, act, rows=rows, gather=True, epilogue=self.epilogue)
-        ops.grouped_linear(act, self.w_down, y, rows=rows)
+        if wide:       # many rows per expert: the inputs in sorted order, then both products by TMA + tcgen05
+            ops.gemm_bf16_tc_grouped(ops.gather_rows(x, rows.token_of), self.w_gate_up, act, rows, self.epilogue)
+            ops.gemm_bf16_tc_grouped(act, self.w_down, y, rows)
+        else:
+            ops.grouped_linear(x, self.w_gate_up, act, rows=rows, gather=True, epilogue=self.epilogue)
+            ops.grouped_linear(act, self.w_down, y, rows=rows)
         ops.route_combine(y, x, ids, weights, rows, out)
         return out
 
