@@ -993,12 +993,19 @@ CO_EXPORT int coheryn_gemm_bf16_tc_grouped(const void* x, const void* w, void* o
   if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_tc_grouped: gated epilogue needs an even number of rows");
   if (!co_epilogue_known(epilogue)) CO_FAIL("gemm_bf16_tc_grouped: unknown epilogue %d", epilogue);
   if (!tile_group || !tile_row0 || !offsets || !n_tiles || !status) CO_FAIL("gemm_bf16_tc_grouped: the tile lists are missing");
-  const int bn = N >= 192 ? 256 : (N >= 96 ? 128 : 64);
+  int bn = N >= 192 ? 256 : (N >= 96 ? 128 : 64);
+  const bool narrow = g_bn == 128 && bn > 128;         // the tuning switch; the W map's box is the tile that runs
+  if (narrow) bn = 128;
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, (long)G * N, K, K, bn))
     CO_FAIL("gemm_bf16_tc_grouped: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d G=%d ldx=%ld)", M, N, K, G, ldx);
   const GroupTiles gt{tile_group, tile_row0, offsets, n_tiles, N};
-  if (bn == 256) return launch_tc_grouped<256, 4>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
+  // Two stages leave room for two CTAs per SM (2 x 256 accumulator columns fill the tensor memory): one's epilogue runs
+  // under the other's main loop, which this kernel of one tile per CTA cannot do by itself.  (The tuning switch picks 4 or 3.)
+  if (bn == 256 && g_stages == 4) return launch_tc_grouped<256, 4>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
+  if (bn == 256 && g_stages == 3) return launch_tc_grouped<256, 3>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
+  if (narrow) return launch_tc_grouped<128, 3>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
+  if (bn == 256) return launch_tc_grouped<256, 2>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
   if (bn == 128) return launch_tc_grouped<128, 6>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
   return launch_tc_grouped<64, 8>(mx, mw, out, out_dtype, M, N, K, ldo, epilogue, status, gt, max_tiles, stream);
 }

@@ -100,6 +100,68 @@ scaled_add_norm_kernel(float* __restrict__ x, const float* __restrict__ parts, i
   }
 }
 
+// The same with the row in registers: H a multiple of 4 and at most 256 * 4 * VPT, every pointer and stride on 16-byte
+// boundaries.  Each global value is read once with 16-byte loads; the weights, which no earlier kernel writes, are
+// requested before the wait for the predecessor.  d is summed part by part from 0 as above.
+__device__ __forceinline__ void san_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void san_store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const unsigned*>(&lo);
+  u.y = *reinterpret_cast<const unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TO, int VPT>
+__global__ void __launch_bounds__(256)
+scaled_add_norm_vec_kernel(float* __restrict__ x, const float* __restrict__ parts, int P, long part_stride, long row_stride,
+                           float alpha, int mode, const void* __restrict__ w, int w_dtype, float eps,
+                           TO* __restrict__ out_cast, int H) {
+  __shared__ float scratch[33];
+  co_pdl_launch_dependents();
+  const int H4 = H >> 2;
+  float4 wv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int j = threadIdx.x + i * 256;
+    if (j < H4) {
+      if (w_dtype == CO_F32) wv[i] = reinterpret_cast<const float4*>(w)[j];
+      else wv[i] = make_float4(co_load_any(w, w_dtype, 4 * j), co_load_any(w, w_dtype, 4 * j + 1), co_load_any(w, w_dtype, 4 * j + 2),
+                               co_load_any(w, w_dtype, 4 * j + 3));
+    }
+  }
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  float* xr = x + t * H;
+  float4 xv[VPT], v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int j = threadIdx.x + i * 256;
+    if (j < H4) {
+      xv[i] = reinterpret_cast<const float4*>(xr)[j];
+      float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < P; ++p) {
+        const float4 a = reinterpret_cast<const float4*>(parts + (size_t)p * part_stride + t * row_stride)[j];
+        d.x += a.x; d.y += a.y; d.z += a.z; d.w += a.w;
+      }
+      v[i] = mode == 0 ? make_float4(fmaf(alpha, xv[i].x, d.x), fmaf(alpha, xv[i].y, d.y), fmaf(alpha, xv[i].z, d.z), fmaf(alpha, xv[i].w, d.w)) : d;
+      ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+  }
+  const float inv = 1.0f / sqrtf(co_block_sum(ss, scratch) / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int j = threadIdx.x + i * 256;
+    if (j < H4) {
+      float4 o = make_float4(v[i].x * inv * wv[i].x, v[i].y * inv * wv[i].y, v[i].z * inv * wv[i].z, v[i].w * inv * wv[i].w);
+      if (mode != 0) { o.x += xv[i].x; o.y += xv[i].y; o.z += xv[i].z; o.w += xv[i].w; }
+      reinterpret_cast<float4*>(xr)[j] = o;
+      if (out_cast) san_store4(out_cast + t * H + 4 * (size_t)j, o);
+    }
+  }
+}
+
 template <typename TZ, typename TW, typename TO>
 __global__ void gated_table_mul_kernel(const TZ* __restrict__ z, long ldz, const TW* __restrict__ table, long ldt, int col0,
                                        const int* __restrict__ ids, TO* __restrict__ out, int T, int n, int V) {
@@ -168,9 +230,24 @@ CO_EXPORT int coheryn_scaled_add_norm(float* x, const float* parts, int P, long 
     co_launch(kern, dim3(n), dim3(256), smem, stream, x, parts, P, part_stride, row_stride, alpha, mode, w, w_dtype, eps, \
               (TO*)out_cast, H);                                                                               \
   }
-  if (out_cast && out_dtype == CO_BF16) GO(__nv_bfloat16)
-  else if (!out_cast || out_dtype == CO_F32) GO(float)
-  else CO_FAIL("scaled_add_norm: unknown output dtype %d", out_dtype);
+  const bool aligned = H % 4 == 0 && H <= 8192 && part_stride % 4 == 0 && row_stride % 4 == 0 && ((uintptr_t)x & 15) == 0 &&
+                       ((uintptr_t)parts & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out_cast & 15) == 0;
+#define VEC(TO, VPT)                                                                                                      \
+  co_launch(scaled_add_norm_vec_kernel<TO, VPT>, dim3(n), dim3(256), 0, stream, x, parts, P, part_stride, row_stride, alpha, mode, w, \
+            w_dtype, eps, (TO*)out_cast, H)
+#define VECS(TO)                                                                                                          \
+  {                                                                                                                       \
+    if (H <= 1024) VEC(TO, 1); else if (H <= 2048) VEC(TO, 2); else if (H <= 4096) VEC(TO, 4); else VEC(TO, 8);          \
+  }
+  if (out_cast && out_dtype != CO_BF16 && out_dtype != CO_F32) CO_FAIL("scaled_add_norm: unknown output dtype %d", out_dtype);
+  if (aligned) {
+    if (out_cast && out_dtype == CO_BF16) VECS(__nv_bfloat16)
+    else VECS(float)
+  }
+  else if (out_cast && out_dtype == CO_BF16) GO(__nv_bfloat16)
+  else GO(float)
+#undef VECS
+#undef VEC
 #undef GO
   CO_CHECK_LAUNCH("scaled_add_norm");
   return 0;
