@@ -373,9 +373,46 @@ __global__ void __launch_bounds__(256)
 route_combine_kernel(const float* __restrict__ y, long ldy, const TH* __restrict__ h, long ldh, const int* __restrict__ ids,
                      const float* __restrict__ weights, const int* __restrict__ row_of, int top, int E, float* __restrict__ out,
                      int H) {
+  constexpr int KEEP = 64;                    // choices whose rows and weights are looked up once, into shared memory
+  __shared__ int row_s[KEEP];
+  __shared__ float w_s[KEEP];
   co_pdl_launch_dependents();
   co_pdl_wait();
   const size_t t = blockIdx.x;
+  if (top <= KEEP) {
+    if ((int)threadIdx.x < top) {
+      const int e = ids[t * top + threadIdx.x];
+      row_s[threadIdx.x] = e < E ? row_of[t * top + threadIdx.x] : -1;      // -1: the token's own input
+      w_s[threadIdx.x] = weights[t * top + threadIdx.x];
+    }
+    __syncthreads();
+    const bool wide = (H & 3) == 0 && (ldy & 3) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    if (wide) {          // four columns a thread, the rows of all choices requested before any is used
+      for (int j = 4 * threadIdx.x; j < H; j += 4 * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 own = make_float4(co_to_float(h[t * ldh + j]), co_to_float(h[t * ldh + j + 1]), co_to_float(h[t * ldh + j + 2]),
+                                       co_to_float(h[t * ldh + j + 3]));
+#pragma unroll 4
+        for (int k = 0; k < top; ++k) {
+          const int r = row_s[k];
+          const float4 v = r >= 0 ? *reinterpret_cast<const float4*>(y + (size_t)r * ldy + j) : own;
+          const float w = w_s[k];
+          acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+        }
+        *reinterpret_cast<float4*>(out + t * H + j) = acc;
+      }
+      return;
+    }
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+      float acc = 0.f;
+      for (int k = 0; k < top; ++k) {
+        const int r = row_s[k];
+        acc = fmaf(w_s[k], r >= 0 ? y[(size_t)r * ldy + j] : co_to_float(h[t * ldh + j]), acc);
+      }
+      out[t * H + j] = acc;
+    }
+    return;
+  }
   for (int j = threadIdx.x; j < H; j += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {

@@ -77,6 +77,8 @@ def rotary_frequencies(rot):
 
 def rotate(v, positions, rot):
     """v [T, ..., n]: the first rot.dims channels of the last axis turn by position (pairs i, i + dims/2)."""
+    if rot is None or v.shape[-1] == 0:            # a mixer without a rotated part
+        return v
     dims = rot["dims"]
     half = dims // 2
     f, amp = rotary_frequencies(rot)

@@ -131,7 +131,8 @@ def test_pair_row_embedding_in_portions(dtype, buckets, mul_prev, mul_cur, width
 
 
 # ------------------------------------------------------------------------------ norms on the stream
-@pytest.mark.parametrize("rows,width,parts", [(5, 64, 1), (70, 100, 3), (9, 256, 2), (3, 8192, 1), (300, 80, 2)])
+@pytest.mark.parametrize("rows,width,parts", [(5, 64, 1), (70, 100, 3), (9, 256, 2), (3, 8192, 1), (300, 80, 2), (4, 99, 2), (2, 8200, 1),
+                                              (6, 2052, 1)])
 @pytest.mark.parametrize("alpha", [1.0, 2.5])
 def test_norm_after_the_sum_and_normalised_summand(rows, width, parts, alpha):
     from coheryn_ai_studio_b200 import ops
@@ -178,7 +179,7 @@ def test_router_choices_and_weights(outputs, identity, groups, keep, top, correc
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width,ff,experts,identity,groups,keep,top,T", [(64, 32, 6, 2, 4, 2, 3, 300), (100, 50, 5, 1, 3, 2, 2, 77),
                                                                           (64, 48, 4, 0, 1, 1, 1, 1), (128, 64, 8, 0, 2, 1, 4, 9),
-                                                                          (40, 30, 3, 0, 1, 1, 3, 130), (256, 136, 5, 1, 1, 1, 2, 700),
+                                                                          (40, 30, 3, 0, 1, 1, 3, 130), (256, 136, 5, 1, 1, 1, 2, 700), (30, 20, 3, 1, 2, 1, 2, 50),
                                                                           (64, 200, 9, 0, 3, 1, 2, 1100)])
 def test_routed_experts_equal_the_plain_experts(dtype, width, ff, experts, identity, groups, keep, top, T):
     """The part alone: tokens of a step sorted by expert (an expert can get more rows than one tile holds, or none at all),
