@@ -271,9 +271,11 @@ __global__ void __launch_bounds__(256) grouped_simt_kernel(GroupedArgs a) {
 }
 
 // bfloat16 on the tensor cores: a CTA of four warps owns 64 rows x 64 columns, a warp 16 rows; K in steps of 32 through a
-// double buffer filled by asynchronous 16-byte copies (K a multiple of 8, rows of A and W on 16-byte boundaries).
+// ring of four stages filled by asynchronous 16-byte copies (K a multiple of 8, rows of A and W on 16-byte boundaries).
 typedef __nv_bfloat16 bf16;
 constexpr int TBM = 64, TBN = 64, TBK = 32, TLD = TBK + 8;
+// TNS, the stages of the ring: 4 for few rows (the matrices stream from memory once, three loads in flight per CTA keep the
+// memory busy), 3 for many (the tiles are reused from L2, and 30 KB instead of 40 leave room for more CTAs).
 
 __device__ __forceinline__ void g_ldsm_x4(unsigned (&r)[4], const void* p) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(p);
@@ -288,10 +290,10 @@ __device__ __forceinline__ void g_cp_async16(void* dst, const void* src, int byt
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a), "l"(src), "r"(bytes) : "memory");
 }
 
-template <typename TO>
+template <typename TO, int TNS>
 __global__ void __launch_bounds__(128) grouped_mma_kernel(GroupedArgs a) {
-  __shared__ __align__(16) bf16 As[2][TBM][TLD];
-  __shared__ __align__(16) bf16 Bs[2][TBN][TLD];
+  __shared__ __align__(16) bf16 As[TNS][TBM][TLD];
+  __shared__ __align__(16) bf16 Bs[TNS][TBN][TLD];
   __shared__ int arow_s[TBM];
   co_pdl_launch_dependents();
   co_pdl_wait();
@@ -327,13 +329,18 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(GroupedArgs a) {
 #pragma unroll
   for (int nt = 0; nt < TBN / 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
   const int steps = (K + TBK - 1) / TBK;
-  load(0, 0);
-  for (int s = 0; s < steps; ++s) {
-    if (s + 1 < steps) load((s + 1) & 1, (s + 1) * TBK);
+  // one group is committed per stage, also an empty one past the end, so that "all but the last TNS - 2 groups" always
+  // means "stage s has landed"
+  for (int s = 0; s < TNS - 1; ++s) {
+    if (s < steps) load(s, s * TBK);
     else asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
-    __syncthreads();
-    const int buf = s & 1;
+  }
+  for (int s = 0; s < steps; ++s) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(TNS - 2) : "memory");
+    __syncthreads();             // stage s is visible to all, and all have finished with stage s - 1, whose buffer is filled next
+    if (s + TNS - 1 < steps) load((s + TNS - 1) % TNS, (s + TNS - 1) * TBK);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    const int buf = s % TNS;
 #pragma unroll
     for (int kk = 0; kk < TBK; kk += 16) {
       unsigned af[4];
@@ -346,7 +353,6 @@ __global__ void __launch_bounds__(128) grouped_mma_kernel(GroupedArgs a) {
         g_mma16816(acc[nt + 1], af, b[2], b[3]);
       }
     }
-    __syncthreads();
   }
   TO* C = (TO*)a.C + (size_t)g * a.c_col;
 #pragma unroll
@@ -483,9 +489,15 @@ CO_EXPORT int coheryn_grouped_linear(const void* A, int a_dtype, long lda, long 
                   w_group % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0;
   if (tc) {
     dim3 grid((N + TBN - 1) / TBN, tiles);
-    if (c_dtype == CO_BF16) co_launch(grouped_mma_kernel<bf16>, grid, dim3(128), 0, stream, a);
-    else if (c_dtype == CO_F32) co_launch(grouped_mma_kernel<float>, grid, dim3(128), 0, stream, a);
-    else CO_FAIL("grouped_linear: unknown output dtype %d", c_dtype);
+    const bool few = M <= (routed ? 1024 : 256);        // rows in all: pairs of a routed step, tokens otherwise
+    if (c_dtype != CO_BF16 && c_dtype != CO_F32) CO_FAIL("grouped_linear: unknown output dtype %d", c_dtype);
+    if (c_dtype == CO_BF16) {
+      if (few) co_launch(grouped_mma_kernel<bf16, 4>, grid, dim3(128), 0, stream, a);
+      else co_launch(grouped_mma_kernel<bf16, 3>, grid, dim3(128), 0, stream, a);
+    } else {
+      if (few) co_launch(grouped_mma_kernel<float, 4>, grid, dim3(128), 0, stream, a);
+      else co_launch(grouped_mma_kernel<float, 3>, grid, dim3(128), 0, stream, a);
+    }
     CO_CHECK_LAUNCH("grouped_mma");
     return 0;
   }
