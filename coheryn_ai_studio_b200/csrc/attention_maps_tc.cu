@@ -71,7 +71,11 @@ struct MapsArgs {
   int table_cache;      // block-table entries a CTA of the prompt kernel may keep in shared memory
   float scale_log2, lambda, eps, out_scale;
   const float* sink_scores;     // [heads]: the sink's score per head (null: 0)
+  const float* gates; long gates_ld;   // [tokens][heads] (row stride gates_ld): head h's output times sigmoid(gates[t, h]) (null: none)
 };
+__device__ __forceinline__ float gate_of(const MapsArgs& A, size_t token, int h) {
+  return A.gates ? 1.0f / (1.0f + expf(-A.gates[token * A.gates_ld + h])) : 1.0f;
+}
 // the sink's score of head h in the log2 domain
 __device__ __forceinline__ float sink_log2(const MapsArgs& A, int h) {
   return A.sink_scores ? A.sink_scores[h] * 1.4426950408889634f : 0.f;
@@ -375,6 +379,7 @@ __global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kerne
       factor *= 1.0f / sqrtf(quad_sum(ss) / (float)DV + A.eps);
     }
     if (row < rows) {
+      factor *= gate_of(A, (size_t)(q0 + tile * BM + row), h);
       bf16* orow = A.out + (size_t)(q0 + tile * BM + row) * A.ldo + (size_t)h * DV + vc * DVC + 2 * (lane & 3);
 #pragma unroll
       for (int nt = 0; nt < OT; ++nt)
@@ -530,7 +535,7 @@ __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const flo
       acc[n] = fmaf(coef_s[m], a, acc[n]);
     }
   }
-  float factor = A.out_scale;
+  float factor = A.out_scale * gate_of(A, (size_t)q0, h);
   if (A.head_norm) {
     float ss = 0.f;
     int n = 0;
@@ -571,13 +576,14 @@ CO_EXPORT long coheryn_maps_scratch_floats(int B, int nh, int max_kv_len, int wi
 
 // q [T, nh * maps * dk], out [T, nh * dv]: bfloat16.  The rows of request r are cu_q[r] .. cu_q[r+1], consecutive positions
 // that end at kv_lens[r] - 1.  max_q_len, max_kv_len: host copies of the longest portion and context.  any_single /
-// any_longer: whether some request brings one token / more than one.
+// any_longer: whether some request brings one token / more than one.  gates (null: none): float32 [T, nh] with row stride
+// gates_ld; head h's output of token t is multiplied by sigmoid(gates[t, h]).
 CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, long ldo, const void* k_cache, const void* v_cache,
                                           const int* block_tables, int max_blocks, const int* cu_q, const int* kv_lens, int B,
                                           int nh, int nkv, int page_size, int window, int chunk, int sink, float scale,
                                           float lambda, int head_norm, float eps, float out_scale, int max_q_len, int max_kv_len,
                                           int any_single, int any_longer, float* scratch, long scratch_floats,
-                                          const float* sink_scores, cudaStream_t stream) {
+                                          const float* sink_scores, const float* gates, long gates_ld, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (nkv <= 0 || nh % nkv) CO_FAIL("attention_maps_bf16: %d heads do not group over %d kv heads", nh, nkv);
   if ((ldq & 7) || (ldo & 1) || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
@@ -587,7 +593,7 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
   const bool decode = any_single && group <= 16;
   MapsArgs A{(const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q,
              kv_lens, nh, nkv, page_size, window, chunk, sink, head_norm, decode ? 1 : 0, 0,
-             scale * 1.4426950408889634f, lambda, eps, out_scale, sink_scores};
+             scale * 1.4426950408889634f, lambda, eps, out_scale, sink_scores, gates, gates_ld};
   if (any_longer || !decode) {
     int visible = max_kv_len;                              // the most keys a row can see
     if (chunk > 0 && chunk < visible) visible = chunk;

@@ -10,7 +10,9 @@
 //                         mode 1: x <- x + d / rms(d) * w                        (a normalised summand)
 //                         d the sum of P float32 parts in order; x is written back in float32 and, when asked, as a
 //                         copy in the compute dtype that the next matrix products read;
-//   * gated_table_mul:    out[t, j] = gelu_tanh(z[t, j]) * table[id_t, col0 + j].
+//   * gated_table_mul:    out[t, j] = gelu_tanh(z[t, j]) * table[id_t, col0 + j];
+//   * copy_head_columns:  a block of columns per head from one matrix into another (or one block into every head's);
+//   * head_gate:          every head's columns times the sigmoid of the head's logit.
 //
 // rms(v) = sqrt(mean(v^2) + eps).  Sums over a row are trees of fixed shape: a row's result does not depend on the
 // other rows of the step.
@@ -175,7 +177,56 @@ __global__ void gated_table_mul_kernel(const TZ* __restrict__ z, long ldz, const
   out[i] = co_from_float<TO>(co_gelu_tanh(co_to_float(z[(size_t)t * ldz + j])) * co_to_float(table[(size_t)id * ldt + col0 + j]));
 }
 
+// dst[t, h * dst_head + dst_off + j] = src[t, h * src_head + src_off + j] for j < n, 16-bit elements (src_head 0: the same
+// columns for every head).
+__global__ void copy_head_columns_kernel(const unsigned short* __restrict__ src, long src_ld, long src_head, long src_off,
+                                         unsigned short* __restrict__ dst, long dst_ld, long dst_head, long dst_off, int n, int H,
+                                         long total) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int j = (int)(i % n), h = (int)((i / n) % H);
+  const long t = i / ((long)n * H);
+  dst[t * dst_ld + h * dst_head + dst_off + j] = src[t * src_ld + h * src_head + src_off + j];
+}
+
+// x[t, h * n + j] *= sigmoid(g[t, h]) in place; g float32 with row stride ldg.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, long ldx, const float* __restrict__ g, long ldg, int n, int H, long total) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int j = (int)(i % n), h = (int)((i / n) % H);
+  const long t = i / ((long)n * H);
+  const float f = 1.0f / (1.0f + expf(-g[t * ldg + h]));
+  T* p = x + t * ldx + (long)h * n + j;
+  *p = co_from_float<T>(co_to_float(*p) * f);
+}
+
 }  // namespace
+
+CO_EXPORT int coheryn_copy_head_columns(const void* src, long src_ld, long src_head, long src_off, void* dst, long dst_ld,
+                                        long dst_head, long dst_off, int n, int H, int T, cudaStream_t stream) {
+  const long total = (long)T * H * n;
+  if (total <= 0) return 0;
+  co_launch(copy_head_columns_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const unsigned short*)src, src_ld,
+            src_head, src_off, (unsigned short*)dst, dst_ld, dst_head, dst_off, n, H, total);
+  CO_CHECK_LAUNCH("copy_head_columns");
+  return 0;
+}
+
+CO_EXPORT int coheryn_head_gate(void* x, int dtype, long ldx, const float* g, long ldg, int n, int H, int T, cudaStream_t stream) {
+  const long total = (long)T * H * n;
+  if (total <= 0) return 0;
+  dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == CO_BF16) co_launch(head_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, ldx, g, ldg, n, H, total);
+  else if (dtype == CO_F32) co_launch(head_gate_kernel<float>, grid, dim3(256), 0, stream, (float*)x, ldx, g, ldg, n, H, total);
+  else CO_FAIL("head_gate: unknown dtype %d", dtype);
+  CO_CHECK_LAUNCH("head_gate");
+  return 0;
+}
 
 // table [V, H], pair [buckets + 1, H] (null: no pair rows) of one dtype; out float32 [T, H]; out_cast (null or [T, H] of
 // out_dtype); w (null: no norm) [H].  mul_prev and mul_cur must lie in [0, buckets).

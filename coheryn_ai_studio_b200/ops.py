@@ -1182,15 +1182,19 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
                    num_heads: int, num_kv_heads: int, dk: int, dv: int, maps: int, page_size: int, window: Optional[int],
                    chunk: Optional[int], sink: bool, scale: float, lam: float, head_norm: bool, eps: float,
                    out_scale: float, force_simple: bool = False, sink_scores: Optional[torch.Tensor] = None,
-                   values_in_keys: bool = False) -> None:
+                   values_in_keys: bool = False, head_gates: Optional[torch.Tensor] = None) -> None:
     """Attention of every token of the step over its request's cache pages of ``group`` with ``maps`` score maps per
     head (output a_0 - lam * a_1 for two), a mask by chunks (``chunk``: position i sees j <= i with i // chunk ==
     j // chunk), by a window or causal, an optional sink term in the softmax's denominator, the head's output divided
     by its root mean square over dv (``head_norm``) and multiplied by ``out_scale``.  q [T, heads * maps * dk],
     out [T, heads * dv]; float32 arithmetic on either storage type.  ``sink_scores`` (float32 [heads]): the sink's score
     per head instead of 0.  ``values_in_keys``: the values are the first dv channels of the key rows (``v_cache`` is not
-    read)."""
+    read).  ``head_gates`` (float32 [T, heads]): head h's output of token t is multiplied by sigmoid(head_gates[t, h])."""
     block_tables = step.block_tables[group]
+    if head_gates is not None:
+        _dev(head_gates)
+        _f32(head_gates, "head_gates")
+        assert head_gates.shape == (q.shape[0], num_heads)
     if sink_scores is not None:
         _dev(sink_scores)
         assert sink and sink_scores.dtype == torch.float32 and sink_scores.is_contiguous() and sink_scores.numel() == num_heads
@@ -1224,7 +1228,8 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
             c_int(page_size), c_int(window or 0), c_int(chunk or 0), c_int(1 if sink else 0), c_float(scale), c_float(lam),
             c_int(1 if head_norm else 0), c_float(eps), c_float(out_scale), c_int(max(q_lens)), c_int(step.max_kv_len),
             c_int(1 if any(n == 1 for n in q_lens) else 0), c_int(1 if any(n > 1 for n in q_lens) else 0), _ptr(scratch),
-            c_long(floats), _ptr(sink_scores), _stream()))
+            c_long(floats), _ptr(sink_scores), _ptr(head_gates), c_long(head_gates.stride(0) if head_gates is not None else 0),
+            _stream()))
         return
     lib = variants()
     _check(lib, lib.coheryn_attention_maps(
@@ -1233,6 +1238,8 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
         c_int(num_heads), c_int(num_kv_heads), c_int(dk), c_int(dv), c_int(maps), c_int(page_size), c_int(window or 0),
         c_int(chunk or 0), c_int(1 if sink else 0), c_float(scale), c_float(lam), c_int(1 if head_norm else 0), c_float(eps),
         c_float(out_scale), _ptr(sink_scores), c_int(1 if values_in_keys else 0), _stream()))
+    if head_gates is not None:
+        head_gate(out, head_gates, num_heads)
 
 
 # ------------------------------------------------------------------------------------
@@ -1305,6 +1312,37 @@ def gated_table_mul(z: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.
     _check(lib, lib.coheryn_gated_table_mul(_ptr(z), c_int(_code(z)), c_long(z.stride(0)), _ptr(table), c_int(_code(table)),
                                             c_long(table.stride(0)), c_int(col0), _ptr(ids), _ptr(out), c_int(T), c_int(n),
                                             c_int(table.shape[0]), _stream()))
+
+
+def copy_head_columns(src: torch.Tensor, src_head: int, src_off: int, dst: torch.Tensor, dst_head: int, dst_off: int, n: int,
+                      heads: int) -> None:
+    """dst[t, h * dst_head + dst_off + j] = src[t, h * src_head + src_off + j] for j < n and every head h (``src_head`` 0:
+    the same block for every head); matrices of 16-bit elements with contiguous rows."""
+    _dev(src, dst)
+    T = src.shape[0]
+    assert src.dtype == dst.dtype and src.element_size() == 2 and src.stride(1) == 1 and dst.stride(1) == 1 and dst.shape[0] == T
+    assert (heads - 1) * src_head + src_off + n <= src.shape[1] and (heads - 1) * dst_head + dst_off + n <= dst.shape[1]
+    lib = core()
+    _check(lib, lib.coheryn_copy_head_columns(_ptr(src), c_long(src.stride(0)), c_long(src_head), c_long(src_off), _ptr(dst),
+                                              c_long(dst.stride(0)), c_long(dst_head), c_long(dst_off), c_int(n), c_int(heads),
+                                              c_int(T), _stream()))
+
+
+def head_gate(x: torch.Tensor, logits: torch.Tensor, heads: int) -> None:
+    """In place: the columns of head h of ``x`` [T, heads * n] times sigmoid(logits[t, h]); ``logits`` float32 [T, heads]."""
+    _dev(x, logits)
+    _f32(logits, "logits")
+    T = x.shape[0]
+    assert x.stride(1) == 1 and logits.stride(1) == 1 and x.shape[1] % heads == 0 and logits.shape == (T, heads)
+    lib = core()
+    _check(lib, lib.coheryn_head_gate(_ptr(x), c_int(_code(x)), c_long(x.stride(0)), _ptr(logits), c_long(logits.stride(0)),
+                                      c_int(x.shape[1] // heads), c_int(heads), c_int(T), _stream()))
+
+
+# A latent attention expands the cached rows of whole prompts into keys and values per head when the step brings at
+# least this many tokens and attending in the latent space would multiply at least RATIO times the channels per score.
+LATENT_EXPAND_MIN_TOKENS = int(os.environ.get("COHERYN_LATENT_EXPAND_MIN_TOKENS", "512"))
+LATENT_EXPAND_RATIO = float(os.environ.get("COHERYN_LATENT_EXPAND_RATIO", "1.5"))
 
 
 # ------------------------------------------------------------------------------------

@@ -9,6 +9,7 @@ o_h = sum_t P_t V[t, g]; y = W_o o (+ b_o).  A ``window`` keeps only the last
 """
 from __future__ import annotations
 
+import types
 from typing import Dict, Optional
 
 import torch
@@ -432,15 +433,34 @@ class LatentAttention(Mixer):
         # uk [heads * dim, rank] applied as uk_h^T: per head a matrix [rank, dim]; uv per head [dv, rank]
         self.w_uk = tensors["uk"].view(H, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = tensors["uv"].view(H, self.dv, self.rank).contiguous()
+        self.w_uk_rows = tensors["uk"].view(H, self.dim, self.rank).contiguous()      # uk_h itself: keys per head from latent rows
         self.w_o = tensors["o"]
         self.sink_scores = tensors["sink"].to(torch.float32).contiguous() if self.sink else None
 
     def output_weights(self):
         return [self.w_o]
 
-    def _queries(self, x: torch.Tensor, step: StepContext, cache: LayerCache):
+    def _expands(self, step: StepContext) -> bool:
+        """Whether this step's attention runs over keys and values EXPANDED per head instead of in the latent space.
+        The latent form reads one row per position for all heads, which is what decoding wants, but multiplies
+        ``rank + rd`` and ``rank`` channels per score where expanded keys and values take ``dim + rd`` and ``dv``.  For
+        whole prompts (every request of the step starts at position 0, so the step's own rows are all the keys there
+        are) of enough tokens, in bfloat16, the rows are expanded through uk and uv and attended with ``heads`` key
+        heads by the same kernel."""
+        dk = self.dim + self.rd
+        q, kv = getattr(step, "q_lens", None), getattr(step, "kv_lens_host", None)
+        if (self.runtime.dtype != torch.bfloat16 or not ops.MAPS_TC or not q or not kv or len(q) != len(kv)
+                or any(a != b or a < 2 for a, b in zip(q, kv))):
+            return False
+        if dk % 16 or self.dv % 16 or self.rank % 8 or self.row % 8 or not 16 <= dk <= 256 or not 16 <= self.dv <= 256:
+            return False
+        latent = self.row + self.rank * (2 if self.rank > 256 else 1)
+        return step.num_tokens >= ops.LATENT_EXPAND_MIN_TOKENS and latent >= ops.LATENT_EXPAND_RATIO * (dk + self.dv)
+
+    def _queries(self, x: torch.Tensor, step: StepContext, cache: LayerCache, expand: bool = False):
         """(queries in the latent space [T, heads * (rank + rd)], gate logits float32 [T, heads] or None); the rows of
-        the step written to the cache when the layer owns its keys."""
+        the step written to the cache when the layer owns its keys.  ``expand``: the queries as the projection made
+        them, [T, heads * (dim + rd)] with the rotated parts turned, for keys expanded per head."""
         Attention._check(cache)
         if cache.writes != self.own_kv:
             raise ValueError("a latent attention with a key projection writes its cache; one without reads another's")
@@ -452,8 +472,16 @@ class LatentAttention(Mixer):
             pos.frequency_pairs() if pos is not None else None, pos.rotary_dim if pos is not None else 0,
             pos.amplitude if pos is not None else 1.0, step.slots[cache.group] if self.own_kv else None, cache.k,
             cache.page_size, self.runtime.dtype)
+        gates = proj[:, self.gate_col:self.gate_col + H] if self.gate else None
+        if expand:
+            dk = self.dim + self.rd
+            q_full = torch.empty((x.shape[0], H * dk), dtype=self.runtime.dtype, device=x.device)
+            ops.copy_head_columns(q_plain, self.dim, 0, q_full, dk, 0, self.dim, H)
+            if self.rd:
+                ops.copy_head_columns(q_wide, self.row, self.rank, q_full, dk, self.dim, self.rd, H)
+            return q_full, gates
         ops.grouped_linear(q_plain, self.w_uk, q_wide, a_col=self.dim, c_col=self.row)
-        return q_wide, proj[:, self.gate_col:self.gate_col + H] if self.gate else None
+        return q_wide, gates
 
     def _attend(self, q_wide, gates, out, step: StepContext, cache: LayerCache) -> None:
         H = self.num_heads
@@ -463,8 +491,38 @@ class LatentAttention(Mixer):
                            values_in_keys=True)
         ops.grouped_linear(o_lat, self.w_uv, out, a_col=self.rank, c_col=self.dv, factor=gates, factor_sigmoid=True)
 
+    def _attend_expanded(self, q_full, gates, out, step: StepContext, cache: LayerCache) -> None:
+        """Whole prompts: the step's cached rows (as the cache holds them) become keys [uk_h c | rotated key] and values
+        uv_h c per head, in the layout of pages of ONE position, and the attention with score maps runs over them with
+        ``heads`` key heads, which applies the gates to its float32 results."""
+        H, dk, T = self.num_heads, self.dim + self.rd, q_full.shape[0]
+        rows = ops.gather_rows(cache.k.view(-1, self.row), step.slots[cache.group])          # [T, rank + rd]
+        keys = torch.empty((T, H * dk), dtype=rows.dtype, device=rows.device)
+        values = torch.empty((T, H * self.dv), dtype=rows.dtype, device=rows.device)
+        ops.grouped_linear(rows, self.w_uk_rows, keys, a_col=0, c_col=dk)
+        if self.rd:
+            ops.copy_head_columns(rows, 0, self.rank, keys, dk, self.dim, self.rd, H)
+        ops.grouped_linear(rows, self.w_uv, values, a_col=0, c_col=self.dv)
+        dense = getattr(step, "_dense_tables", None)
+        if dense is None:            # "pages" of one position: request r's position j is row cu_q[r] + j of the step
+            ar = torch.arange(step.max_q_len, dtype=torch.int32, device=rows.device)
+            dense = (step.cu_q[:-1].to(torch.int32).unsqueeze(1) + ar.unsqueeze(0)).contiguous()
+            try:
+                step._dense_tables = dense
+            except AttributeError:
+                pass
+        view = types.SimpleNamespace(block_tables=[dense], token_req=step.token_req, positions=step.positions, cu_q=step.cu_q,
+                                     kv_lens=step.kv_lens, q_lens=step.q_lens, max_kv_len=step.max_kv_len)
+        ops.attention_maps(q_full, out, keys.view(T, H, 1, dk), values.view(T, H, 1, self.dv), view, 0, H, H, dk, self.dv, 1, 1,
+                           None, None, self.sink, self.scale, 0.0, False, self.eps, 1.0, sink_scores=self.sink_scores,
+                           head_gates=gates)
+
     def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
         """The gated heads' outputs in front of the output product into ``outs[0]`` ([T, heads * dv])."""
+        if self._expands(step):
+            q_full, gates = self._queries(x, step, cache, expand=True)
+            self._attend_expanded(q_full, gates, outs[0], step, cache)
+            return
         q_wide, gates = self._queries(x, step, cache)
         self._attend(q_wide, gates, outs[0], step, cache)
 

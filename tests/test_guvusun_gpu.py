@@ -82,7 +82,7 @@ class Rows:
         return types.SimpleNamespace(
             num_requests=len(runs), num_tokens=int(cu[-1]), token_req=dev(req, torch.int32), positions=dev(pos, torch.int32),
             cu_q=dev(cu, torch.int32), kv_lens=dev(kv, torch.int32), block_tables=[dev(tables, torch.int32)],
-            slots=[dev(slots, torch.int32)], q_lens=[n for _, _, n in runs], max_q_len=max(n for _, _, n in runs),
+            slots=[dev(slots, torch.int32)], q_lens=[n for _, _, n in runs], kv_lens_host=kv, max_q_len=max(n for _, _, n in runs),
             max_kv_len=max(kv), prior_positions_settled=True, token_ids=dev(ids, torch.int32) if ids is not None else None,
             state_slots=dev([self.state_slots[r] for r, _, _ in runs], torch.int32), tail=None, tail_rows=None)
 
@@ -263,7 +263,7 @@ def make_mixer(m, width, eps, dtype, W, own=True):
     from coheryn_ai_studio_b200.parts.position import ComputedRope
     rt = Runtime(dtype, torch.device(DEV))
     rot = m["rot"]
-    pos = ComputedRope(rt, rotary_dim=rot["dims"], theta=rot["base"], scaling=rot.get("scaling"))
+    pos = ComputedRope(rt, rotary_dim=rot["dims"], theta=rot["base"], scaling=rot.get("scaling")) if rot is not None else None
     mixer = LatentAttention(rt, width, m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["scale"], eps, sink=True,
                             gate=True, own_kv=own, position=pos)
     mixer.bind({k: dev(v, torch.float32 if k in ("sink", "dkv.norm") else dtype) for k, v in W.items()})
@@ -318,6 +318,55 @@ def test_latent_attention_in_portions_and_decoded(dtype, m, width, page):
     assert at == lengths
 
 
+class expanded_prompts:
+    """Inside: whole prompts of any length expand their latent rows per head (where the sizes allow)."""
+
+    def __init__(self, on=True):
+        self.on = on
+
+    def __enter__(self):
+        from coheryn_ai_studio_b200 import ops
+        self.kept = (ops.LATENT_EXPAND_MIN_TOKENS, ops.LATENT_EXPAND_RATIO)
+        ops.LATENT_EXPAND_MIN_TOKENS, ops.LATENT_EXPAND_RATIO = (2, 0.0) if self.on else (1 << 30, 1e9)
+
+    def __exit__(self, *exc):
+        from coheryn_ai_studio_b200 import ops
+        ops.LATENT_EXPAND_MIN_TOKENS, ops.LATENT_EXPAND_RATIO = self.kept
+
+
+@pytest.mark.parametrize("m,width,page", [MIXERS[0], (shape(3, 32, 16, 32, 96, YARN), 64, 16), (shape(2, 16, 16, 16, 320, YARN), 64, 8),
+                                          (shape(5, 16, 0, 48, 40, {"dims": 0, "base": 10.0}), 96, 16)])
+def test_whole_prompts_attend_over_rows_expanded_per_head(m, width, page):
+    """Two whole prompts in one step take the expanded form (keys uk_h c | rotated key and values uv_h c per head), also in a
+    mixer that reads the first one's rows; their next portions and single tokens attend in the latent space over the same
+    cache.  Both equal the plain mixer."""
+    rng = np.random.default_rng(m["heads"] * 7 + m["kv_rank"])
+    eps, lengths, dtype = 1e-5, [171, 90], torch.bfloat16
+    m = dict(m, rot=None) if m["rot_dim"] == 0 else m
+    m2 = dict(m, heads=m["heads"] + 1, dim=m["dim"] + 16, vdim=16, scale=0.15)
+    W1, W2 = mixer_weights(rng, width, m), mixer_weights(rng, width, m2, own=False)
+    a, b = make_mixer(m, width, eps, dtype, W1), make_mixer(m2, width, eps, dtype, W2, own=False)
+    seqs = []
+    for n in lengths:
+        h = bf(rng.normal(size=(n, width)))
+        y1, kept = plain.latent_attention(h, range(n), W1, "", m, eps, rounder=bf)
+        y2, _ = plain.latent_attention(h * 0.5, range(n), W2, "", m2, eps, shared=kept, rounder=bf)
+        seqs.append((h, y1, y2))
+    cache = Rows(lengths, m["kv_rank"] + m["rot_dim"], page, dtype, seed=width)
+    at = [0, 0]
+    with expanded_prompts():
+        for n0, n1 in ((150, 83), (20, 1), (1, 6)):
+            step = cache.step([(0, at[0], n0), (1, at[1], n1)])
+            assert a._expands(step) == (at == [0, 0]) and b._expands(step) == (at == [0, 0])
+            h = np.concatenate([seqs[0][0][at[0]:at[0] + n0], seqs[1][0][at[1]:at[1] + n1]])
+            for mixer, which, cache_view, scale in ((a, 1, cache.writer, 1.0), (b, 2, cache.reader, 0.5)):
+                got = host(mixer.forward(dev(h * scale, dtype), step, cache_view))
+                want = np.concatenate([seqs[0][which][at[0]:at[0] + n0], seqs[1][which][at[1]:at[1] + n1]])
+                assert np.abs(got - want).max() < 0.03 * max(1.0, np.abs(want).max()), (which, at, np.abs(got - want).max())
+            at = [at[0] + n0, at[1] + n1]
+    assert at == lengths
+
+
 @pytest.mark.parametrize("tensor_cores", [True, False])
 @pytest.mark.parametrize("m,width,page", [MIXERS[0], MIXERS[1], MIXERS[5], (shape(2, 24, 32, 16, 64, {"dims": 32, "base": 10000.0}), 64, 8)])
 def test_one_key_that_stands_out_far_back_and_at_the_borders(tensor_cores, m, width, page):
@@ -339,25 +388,28 @@ def test_one_key_that_stands_out_far_back_and_at_the_borders(tensor_cores, m, wi
     mixer = make_mixer(m, width, eps, dtype, W)
     ops.set_maps_tc(tensor_cores)
     try:
-        for marked in (0, 5, page - 1, page, 63, 64, 127, 128):
-            h = bf(rng.normal(size=(n, width)) * 0.3)
-            h[:, 0], h[:, 1] = 0.0, 1.0
-            h[marked, 0] = 1.0
-            want, (c, _) = plain.latent_attention(h, range(n), W, "", m, eps, rounder=bf)
-            cache = Rows([n], r + rdim, page, dtype, seed=marked)
-            got, at = [], 0
-            for portion in (max(marked + 2, 130), 401 - max(marked + 2, 130), 1, 1, 1, 1, 1, 1, 1, 1, 1, 9, 1):
-                got.append(host(mixer.forward(dev(h[at:at + portion], dtype), cache.step([(0, at, portion)]), cache.writer)))
-                at += portion
-            got = np.concatenate(got)
-            assert at == n and np.abs(got - want).max() < 0.04 * max(1.0, np.abs(want).max()), (marked, np.abs(got - want).max())
-            # the setup itself: with the key the rows differ from those without it by far more than the tolerance
-            h2 = h.copy(); h2[marked, 0] = 0.0
-            without = plain.latent_attention(h2, range(n), W, "", m, eps, rounder=bf)[0]
-            for row in (marked + 1, 300, 400, 401, 409, 419):
-                assert np.abs(want[row] - without[row]).max() > 0.3 * np.abs(want).max(), (marked, row, "the key does not stand out")
-            if marked:
-                assert np.abs(want[marked - 1] - without[marked - 1]).max() == 0.0
+        # with tensor cores once more with the first portion expanded per head
+        for expand in ((False, True) if tensor_cores and (dim + rdim) % 16 == 0 else (False,)):
+            with expanded_prompts(expand):
+                for marked in (0, 5, page - 1, page, 63, 64, 127, 128):
+                    h = bf(rng.normal(size=(n, width)) * 0.3)
+                    h[:, 0], h[:, 1] = 0.0, 1.0
+                    h[marked, 0] = 1.0
+                    want, (c, _) = plain.latent_attention(h, range(n), W, "", m, eps, rounder=bf)
+                    cache = Rows([n], r + rdim, page, dtype, seed=marked)
+                    got, at = [], 0
+                    for portion in (max(marked + 2, 130), 401 - max(marked + 2, 130), 1, 1, 1, 1, 1, 1, 1, 1, 1, 9, 1):
+                        got.append(host(mixer.forward(dev(h[at:at + portion], dtype), cache.step([(0, at, portion)]), cache.writer)))
+                        at += portion
+                    got = np.concatenate(got)
+                    assert at == n and np.abs(got - want).max() < 0.04 * max(1.0, np.abs(want).max()), (marked, np.abs(got - want).max())
+                    # the setup itself: with the key the rows differ from those without it by far more than the tolerance
+                    h2 = h.copy(); h2[marked, 0] = 0.0
+                    without = plain.latent_attention(h2, range(n), W, "", m, eps, rounder=bf)[0]
+                    for row in (marked + 1, 300, 400, 401, 409, 419):
+                        assert np.abs(want[row] - without[row]).max() > 0.3 * np.abs(want).max(), (marked, row, "the key does not stand out")
+                    if marked:
+                        assert np.abs(want[marked - 1] - without[marked - 1]).max() == 0.0
     finally:
         ops.set_maps_tc(True)
 
@@ -421,6 +473,20 @@ def test_whole_prompts(name, dtype, folders, models):
         r = gc.noisy_replay(folders[name], dtype, 128, models(name, dtype))
         r.step([("r", seq, list(range(n)))], end=["r"])
         gc.check_rows(r.rows, folders[name], {"r": seq}, dtype, f"whole {n}")
+
+
+@pytest.mark.parametrize("name", ["G1", "G3"])
+def test_whole_prompts_with_rows_expanded_per_head(name, folders, models):
+    """Whole prompts (also two in one step, with wanted rows everywhere so that the last layer runs whole) through the
+    expanded form of the attention, then more tokens of the same requests through the latent form."""
+    V = vocab(name)
+    seqs = {"a": gc.prompt(71, 140, V), "b": gc.prompt(72, 57, V)}
+    with expanded_prompts():
+        r = gc.noisy_replay(folders[name], "bfloat16", 256, models(name, "bfloat16"))
+        r.step([("a", seqs["a"][:120], list(range(120))), ("b", seqs["b"][:40], list(range(40)))])
+        r.step([("a", seqs["a"][120:139], list(range(19))), ("b", seqs["b"][40:41], [0])])
+        r.step([("a", seqs["a"][139:], [0]), ("b", seqs["b"][41:], list(range(16)))], end=["a", "b"])
+    gc.check_rows(r.rows, folders[name], seqs, "bfloat16", "expanded")
 
 
 def test_layer_outputs_equal_the_plain_layers(folders, models):
