@@ -684,6 +684,28 @@ def guvusun_workload(args) -> int:
             attention("latent_attention_sink", lambda: ops.attention_maps(
                 q, o, kc, None, st, 0, H, 1, row, rank, 1, page, None, None, True, hd ** -0.5, 0.0, False, 1e-6, 1.0,
                 sink_scores=sinks, values_in_keys=True), row + rank, min(row + rank, hd + dv), 2.0 * row * held, 2.0 * T * H * (row + rank))
+            if name == "prefill" and hd % 16 == 0 and dv % 16 == 0 and hd <= 256 and dv <= 256:
+                # what a whole prompt runs instead: its rows expanded per head (keys uk_h c | rotated key, values uv_h c), then the
+                # same kernel with a key head per query head and the gates in its epilogue
+                rows_c, ukr, uvr = b16(T, row), b16(H, dim, rank), b16(H, dv, rank)
+                ke, ve = torch.empty((T, H * hd), dtype=torch.bfloat16, device=dev), torch.empty((T, H * dv), dtype=torch.bfloat16, device=dev)
+
+                def expand():
+                    got = ops.gather_rows(kc.view(-1, row), st.slots[0])
+                    ops.grouped_linear(got, ukr, ke, a_col=0, c_col=hd)
+                    ops.copy_head_columns(got, 0, rank, ke, hd, dim, rd, H)
+                    ops.grouped_linear(got, uvr, ve, a_col=0, c_col=dv)
+                ms = timed(expand)
+                fl = 2.0 * T * H * rank * (dim + dv)
+                out[f"{name}.latent_rows_expanded_per_head"] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                                                                 "of_bf16_peak": round(fl / (ms / 1e3) / flops_peak, 4)}
+                import types
+                dense = types.SimpleNamespace(block_tables=[torch.arange(T, dtype=torch.int32, device=dev).view(1, T)], token_req=st.token_req,
+                                              positions=st.positions, cu_q=st.cu_q, kv_lens=st.kv_lens, q_lens=st.q_lens, max_kv_len=st.max_kv_len)
+                qe, oe, gl = b16(T, H * hd), torch.empty((T, H * dv), dtype=torch.bfloat16, device=dev), f(T, H)
+                attention("attention_sink_expanded_rows", lambda: ops.attention_maps(
+                    qe, oe, ke.view(T, H, 1, hd), ve.view(T, H, 1, dv), dense, 0, H, H, hd, dv, 1, 1, None, None, True, hd ** -0.5, 0.0, False,
+                    1e-6, 1.0, sink_scores=sinks, head_gates=gl), hd + dv, hd + dv, 2.0 * T * H * (hd + dv), 2.0 * T * H * (hd + dv))
             G = 2
             kq, vq = b16(B * per + 1, G, page, hd), b16(B * per + 1, G, page, hd)
             qq, oq = b16(T, H * hd), torch.empty((T, H * hd), dtype=torch.bfloat16, device=dev)
