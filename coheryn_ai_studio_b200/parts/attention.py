@@ -382,7 +382,11 @@ class LatentAttention(Mixer):
     amplitude multiplies cos and sin; ``scale`` is taken as given).  Options: ``sink`` (one more term exp(sink_h) in the
     softmax's denominator with a learned score per head, tensor ``sink``, that carries no value) and ``gate`` (head h's
     output is multiplied by sigmoid(g x)_h, tensor ``g`` [heads, width], the same input as the projections).  A layer
-    without keys of its own reads the rows (latent and rotated key) that an earlier one wrote, with its own uk and uv."""
+    without keys of its own reads the rows (latent and rotated key) that an earlier one wrote, with its own uk and uv.
+
+    Whole prompts (``_expands``) are attended in the EXPANDED form instead: the step's cached rows become keys
+    [uk_h c | rotated key] and values uv_h c per head, which costs ``dim + rd`` and ``dv`` channels per score instead of
+    ``rank + rd`` and ``rank``; the cache and everything that reads it later are the same either way."""
 
     output_parts = 1
 
