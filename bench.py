@@ -630,7 +630,7 @@ def guvusun_config(z):
                   "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}
         layers.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "moe", "expert": {"ff": z["ff"]}, "router": router}})
     return {"architecture": "Guvusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
-            "embedding": {"bigram": {"buckets": z["buckets"], "mul_prev": 127, "mul_cur": 7}}, "token_side": {"dim": z["side_dim"]},
+            "embedding": {"bigram": {"buckets": z["buckets"], "mul_prev": 131, "mul_cur": 11}}, "token_side": {"dim": z["side_dim"]},
             "layers": layers}
 
 
