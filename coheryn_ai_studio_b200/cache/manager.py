@@ -105,24 +105,27 @@ class CacheManager:
         # the writes of padding rows (a decode batch padded up to a captured width).
         for g in self.groups:
             n = g.need
+            if n.stride < 1 or (n.stride > 1 and n.window is not None):
+                raise ValueError("rows that stand for blocks of positions need a positive stride and take no window")
+            rows_pp = n.rows_per_page(self.page_size)      # rows of a page of this group (the books count positions)
             if n.v_head_dim == 0:
                 # no value rows: the mixer reads its values out of the key rows
-                g.tensor = torch.zeros((len(g.entries), 1, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
+                g.tensor = torch.zeros((len(g.entries), 1, num_pages + 1, n.num_kv_heads, rows_pp, n.head_dim),
                                        dtype=dtype, device=device)
                 g.k = [g.tensor[i, 0] for i in range(len(g.entries))]
                 g.v = [None] * len(g.entries)
             elif n.v_head_dim is None or n.v_head_dim == n.head_dim:
-                g.tensor = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
+                g.tensor = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, rows_pp, n.head_dim),
                                        dtype=dtype, device=device)
                 g.k = [g.tensor[i, 0] for i in range(len(g.entries))]
                 g.v = [g.tensor[i, 1] for i in range(len(g.entries))]
             else:
                 # values of another head size than keys: per entry the keys of all pages, then the values
-                rows = (num_pages + 1) * n.num_kv_heads * page_size
+                rows = (num_pages + 1) * n.num_kv_heads * rows_pp
                 g.tensor = torch.zeros((len(g.entries), rows * (n.head_dim + n.v_head_dim)), dtype=dtype, device=device)
-                g.k = [g.tensor[i, :rows * n.head_dim].view(num_pages + 1, n.num_kv_heads, page_size, n.head_dim)
+                g.k = [g.tensor[i, :rows * n.head_dim].view(num_pages + 1, n.num_kv_heads, rows_pp, n.head_dim)
                        for i in range(len(g.entries))]
-                g.v = [g.tensor[i, rows * n.head_dim:].view(num_pages + 1, n.num_kv_heads, page_size, n.v_head_dim)
+                g.v = [g.tensor[i, rows * n.head_dim:].view(num_pages + 1, n.num_kv_heads, rows_pp, n.v_head_dim)
                        for i in range(len(g.entries))]
         reuse = bool(prefix_reuse) and not self._state and all(g.need.window is None for g in self.groups)
         self._lib = host()
@@ -190,7 +193,7 @@ class CacheManager:
 
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * item
+        return sum(-(-len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * item // g.need.stride)
                    for g in self.groups)
 
     # ------------------------------------------------------------------ requests

@@ -17,6 +17,7 @@ from .qwen2 import (ConfigError, Qwen2Config, qwen2_config_from_gguf, qwen2_gguf
 from .kapudra import KapudraConfig, kapudra_model_spec
 from .tutunex import TutunexConfig, tutunex_model_spec
 from .guvusun import GuvusunConfig, guvusun_model_spec
+from .zegelix import ZegelixConfig, zegelix_model_spec
 from .spec import ModelSpec
 
 
@@ -72,7 +73,7 @@ class Architecture:
         needs = []
         for n in model.cache_requirements():      # a mixer made of several asks for a tuple
             needs.extend(n if isinstance(n, (tuple, list)) else [n])
-        kv_elements = sum(n.num_kv_heads * (n.head_dim + n.value_dim) for n in needs if isinstance(n, PagedKV))
+        kv_elements = sum(-(-n.num_kv_heads * (n.head_dim + n.value_dim) // n.stride) for n in needs if isinstance(n, PagedKV))
         state_bytes = 0
         for n in needs:
             if isinstance(n, FixedState):
@@ -190,3 +191,4 @@ register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_model_spe
 register_architecture("Kapudra", KapudraConfig.from_dict, kapudra_model_spec, adapter_id="kapudra-b200-v1")
 register_architecture("Tutunex", TutunexConfig.from_dict, tutunex_model_spec, adapter_id="tutunex-b200-v1")
 register_architecture("Guvusun", GuvusunConfig.from_dict, guvusun_model_spec, adapter_id="guvusun-b200-v1")
+register_architecture("Zegelix", ZegelixConfig.from_dict, zegelix_model_spec, adapter_id="zegelix-b200-v1")

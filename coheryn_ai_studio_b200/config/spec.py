@@ -54,12 +54,15 @@ def prenorm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_no
 
 @dataclass(frozen=True)
 class StreamInject:
-    """Something added to the residual stream right before a schedule entry runs: the embedding
+    """Something done to the residual stream right before a schedule entry runs.  Added to it: the embedding
     output of the step's tokens once more (``embedding``), and row ``vector[1]`` of the tensor
-    named ``vector[0]`` (a [rows, width] tensor of ``ModelSpec.extra_tensors``)."""
+    named ``vector[0]`` (a [rows, width] tensor of ``ModelSpec.extra_tensors``).  Or, instead, ``mix``: the stream is
+    REPLACED by M [x ; x0], x being the stream (with everything pending added), x0 the embedding output of the step's
+    tokens and M the [width, 2 width] tensor of ``ModelSpec.extra_tensors`` that ``mix`` names."""
 
     embedding: bool = False
     vector: Optional[Tuple[str, int]] = None
+    mix: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -123,6 +126,15 @@ class ModelSpec:
                     raise ValueError(
                         f"schedule entry {i} reads the cache of entry {e.cache_from}, "
                         "which owns no cache itself")
+            if e.inject is not None and e.inject.mix is not None:
+                if e.inject.embedding or e.inject.vector is not None:
+                    raise ValueError(f"schedule entry {i}: the stream is either replaced by a mix or added to, not both")
+                shape = self.extra_tensors.get(e.inject.mix, (None,))[0]
+                if shape is None or tuple(shape) != (self.hidden_size, 2 * self.hidden_size):
+                    raise ValueError(f"schedule entry {i} mixes the stream by {e.inject.mix!r}, which is not a "
+                                     f"[{self.hidden_size}, {2 * self.hidden_size}] tensor of the model")
+                if self.embedder is not None:
+                    raise ValueError(f"schedule entry {i}: a mix with the embedding output needs the plain embedding")
             if e.inject is not None and e.inject.vector is not None:
                 name, row = e.inject.vector
                 shape = self.extra_tensors.get(name, (None,))[0]

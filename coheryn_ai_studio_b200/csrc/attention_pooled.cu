@@ -1,0 +1,313 @@
+// Sliding-window attention whose older keys are seen as block means (sm_100a; float32 arithmetic on float32 or bfloat16
+// storage).  Position i sees the positions j with 0 <= i - j < window, and beside them ONE key and value for each block
+// of `pool` consecutive positions that lies wholly before the window: block b (positions b*pool .. b*pool + pool - 1) is
+// seen when b*pool + pool - 1 <= i - window; its key is the mean of the block's keys as the cache holds them, its value
+// the mean of the values.  Positions and blocks share one softmax.  Options, each a parameter:
+//   * rotation of the first `rot` channels of queries and keys (pairs (i, i + rot/2)), and of ALL channels of the values
+//     (pairs (m, m + dv/2), their own frequencies); a head's output at position i is turned back by -i;
+//   * score = (q . k) * scale * temp[head], then cap * tanh(score / cap);
+//   * one more term exp(sink[head]) in the softmax's denominator, without key or value;
+//   * the output multiplied by sigmoid(gate[t, head * dv + c]).
+//
+// Kernels:
+//   * pooled_prepare: rotates q, k, v of every row by its position (angles from float32 frequency pairs high + low, so no
+//                     table bounds the positions), writes k and v to the cache pages and q in the compute dtype;
+//   * pooled_means:   for every block that the step completed, the means of its keys and values, read back from the
+//                     cache in position order, into the block cache: a second set of pages under a block table of its
+//                     own with ceil(page_size / pool) rows per page; block b lives in the page of its LAST position p,
+//                     at row b - floor(page(p) * page_size / pool);
+//   * pooled_attention: one CTA per (row, head): four warps take the keys in turn (a key's place among the row's keys
+//                     decides its warp, so a row's sums do not depend on the batch), online softmax per warp, merged in
+//                     warp order.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void pa_sincos(float p, const float* freq, int i, float& c, float& s) {
+  const float fh = freq[2 * i], fl = freq[2 * i + 1];
+  const float ah = p * fh;
+  const float al = fmaf(p, fh, -ah) + p * fl;      // what the rounding of p * fh lost, and the low part
+  float sh, ch, sl, cl;
+  sincosf(ah, &sh, &ch);
+  sincosf(al, &sl, &cl);
+  c = ch * cl - sh * sl;
+  s = sh * cl + ch * sl;
+}
+
+// grid (T, heads + 2 * kv_heads); proj float32 [T, ld]: queries from column 0, keys from q_cols, values behind them.
+template <typename TT>
+__global__ void pooled_prepare_kernel(const float* __restrict__ proj, long ld, const int* __restrict__ positions,
+                                      const float* __restrict__ freq_k, int rot, const float* __restrict__ freq_v,
+                                      TT* __restrict__ q_out, long ldq, const int* __restrict__ slots, TT* __restrict__ k_cache,
+                                      TT* __restrict__ v_cache, int H, int G, int dk, int dv, int page_size) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  const int unit = blockIdx.y;
+  const float p = (float)positions[t];
+  const float* src;
+  TT* dst;
+  int n, turned;
+  const float* freq;
+  if (unit < H) {
+    src = proj + t * ld + (size_t)unit * dk;
+    dst = q_out + t * ldq + (size_t)unit * dk;
+    n = dk; turned = rot; freq = freq_k;
+  } else {
+    if (!slots) return;
+    const int slot = slots[t];
+    const size_t page = slot / page_size, off = slot % page_size;
+    if (unit < H + G) {
+      const int g = unit - H;
+      src = proj + t * ld + (size_t)H * dk + (size_t)g * dk;
+      dst = k_cache + ((page * G + g) * page_size + off) * dk;
+      n = dk; turned = rot; freq = freq_k;
+    } else {
+      const int g = unit - H - G;
+      src = proj + t * ld + (size_t)(H + G) * dk + (size_t)g * dv;
+      dst = v_cache + ((page * G + g) * page_size + off) * dv;
+      n = dv; turned = freq_v ? dv : 0; freq = freq_v;
+    }
+  }
+  const int half = turned / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float c, s;
+    pa_sincos(p, freq, i, c, s);
+    const float a = src[i], b = src[i + half];
+    dst[i] = co_from_float<TT>(a * c - b * s);
+    dst[i + half] = co_from_float<TT>(b * c + a * s);
+  }
+  for (int i = turned + threadIdx.x; i < n; i += blockDim.x) dst[i] = co_from_float<TT>(src[i]);
+}
+
+// grid (B * per_request, G): candidate `which` of request r is block first + which, first = the first block whose last
+// position the step wrote.
+template <typename TT>
+__global__ void pooled_means_kernel(const TT* __restrict__ k_cache, const TT* __restrict__ v_cache, TT* __restrict__ pk_cache,
+                                    TT* __restrict__ pv_cache, const int* __restrict__ tables, int table_width,
+                                    const int* __restrict__ pool_tables, int pool_table_width, const int* __restrict__ cu_q,
+                                    const int* __restrict__ kv_lens, int per_request, int G, int dk, int dv, int page_size,
+                                    int pool, int pool_rows) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x / per_request, which = blockIdx.x % per_request, g = blockIdx.y;
+  const int p1 = kv_lens[r], p0 = p1 - (cu_q[r + 1] - cu_q[r]);
+  const int b = p0 / pool + which;                       // blocks whose last position is >= p0
+  const long last = (long)b * pool + pool - 1;
+  if (p1 <= p0 || last >= p1) return;
+  const int* table = tables + (size_t)r * table_width;
+  const int lp = (int)(last / page_size);
+  const int row = b - (int)(((long)lp * page_size) / pool);
+  const size_t dst_page = (size_t)pool_tables[(size_t)r * pool_table_width + lp];
+  const float inv = 1.0f / (float)pool;
+  for (int c = threadIdx.x; c < dk + dv; c += blockDim.x) {
+    const bool is_k = c < dk;
+    const int ch = is_k ? c : c - dk, width = is_k ? dk : dv;
+    const TT* cache = is_k ? k_cache : v_cache;
+    float sum = 0.f;
+    for (int j = 0; j < pool; ++j) {
+      const long pos = (long)b * pool + j;
+      const size_t page = (size_t)table[pos / page_size];
+      sum += co_to_float<TT>(cache[((page * G + g) * page_size + (size_t)(pos % page_size)) * width + ch]);
+    }
+    TT* dst = is_k ? pk_cache : pv_cache;
+    dst[((dst_page * G + g) * pool_rows + row) * width + ch] = co_from_float<TT>(sum * inv);
+  }
+}
+
+struct AttnArgs {
+  const void* q; long ldq;
+  void* out; long ldo;
+  const void* k; const void* v; const void* pk; const void* pv;
+  const int* tables; int table_width; const int* pool_tables; int pool_table_width;
+  const int* token_req; const int* positions;
+  const float* temps; const float* sinks; const float* gates; long ldgate;
+  const float* freq_v;
+  int H, G, dk, dv, page_size, window, pool, pool_rows;
+  float scale, cap;
+};
+
+constexpr int PA_WARPS = 4;
+constexpr int PA_MAX_PER_LANE = 8;     // channels per lane: head sizes up to 256
+
+template <typename TT>
+__global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_kernel(AttnArgs A) {
+  extern __shared__ __align__(16) float sm[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  const int h = blockIdx.y, g = h / (A.H / A.G);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int dk = A.dk, dv = A.dv;
+  float* qs = sm;                                  // [dk]
+  float* acc_s = qs + dk;                          // [PA_WARPS][dv]
+  float* ml = acc_s + PA_WARPS * dv;               // [PA_WARPS][2]
+  float* os = ml + 2 * PA_WARPS;                   // [dv]
+  const TT* q = (const TT*)A.q + t * A.ldq + (size_t)h * dk;
+  for (int c = threadIdx.x; c < dk; c += blockDim.x) qs[c] = co_to_float<TT>(q[c]);
+  __syncthreads();
+  const int i = A.positions[t];
+  const int r = A.token_req[t];
+  const int* table = A.tables + (size_t)r * A.table_width;
+  const int lo = A.window > 0 ? max(0, i - A.window + 1) : 0;
+  const int nb = (A.pool > 0 && A.window > 0 && i - A.window + 1 > 0) ? (i - A.window + 1) / A.pool : 0;
+  const int total = nb + (i - lo + 1);
+  const float mult = A.scale * (A.temps ? A.temps[h] : 1.f);
+  float qreg[PA_MAX_PER_LANE], acc[PA_MAX_PER_LANE];
+#pragma unroll
+  for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
+    const int c = lane + 32 * e;
+    qreg[e] = c < dk ? qs[c] : 0.f;
+    acc[e] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int n = warp; n < total; n += PA_WARPS) {
+    const TT* kr;
+    const TT* vr;
+    if (n < nb) {
+      const long last = (long)n * A.pool + A.pool - 1;
+      const int lp = (int)(last / A.page_size);
+      const int row = n - (int)(((long)lp * A.page_size) / A.pool);
+      const size_t page = (size_t)A.pool_tables[(size_t)r * A.pool_table_width + lp];
+      const size_t at = (page * A.G + g) * A.pool_rows + row;
+      kr = (const TT*)A.pk + at * dk;
+      vr = (const TT*)A.pv + at * dv;
+    } else {
+      const int pos = lo + (n - nb);
+      const size_t page = (size_t)table[pos / A.page_size];
+      const size_t at = (page * A.G + g) * A.page_size + (size_t)(pos % A.page_size);
+      kr = (const TT*)A.k + at * dk;
+      vr = (const TT*)A.v + at * dv;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
+      const int c = lane + 32 * e;
+      if (c < dk) s = fmaf(qreg[e], co_to_float<TT>(kr[c]), s);
+    }
+    s = co_warp_sum(s) * mult;
+    if (A.cap > 0.f) s = A.cap * tanhf(s / A.cap);
+    const float m_new = fmaxf(m, s);
+    const float f = expf(m - m_new), w = expf(s - m_new);      // exp(-inf) = 0 for the first key
+    l = l * f + w;
+#pragma unroll
+    for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
+      const int c = lane + 32 * e;
+      if (c < dv) acc[e] = fmaf(w, co_to_float<TT>(vr[c]), acc[e] * f);
+    }
+    m = m_new;
+  }
+#pragma unroll
+  for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
+    const int c = lane + 32 * e;
+    if (c < dv) acc_s[warp * dv + c] = acc[e];
+  }
+  if (lane == 0) { ml[2 * warp] = m; ml[2 * warp + 1] = l; }
+  __syncthreads();
+  // merge in warp order; the sink joins the denominator once
+  float top = A.sinks ? A.sinks[h] : -INFINITY;
+#pragma unroll
+  for (int w = 0; w < PA_WARPS; ++w) top = fmaxf(top, ml[2 * w]);
+  float denom = A.sinks ? expf(A.sinks[h] - top) : 0.f;
+  float fw[PA_WARPS];
+#pragma unroll
+  for (int w = 0; w < PA_WARPS; ++w) {
+    fw[w] = ml[2 * w] == -INFINITY ? 0.f : expf(ml[2 * w] - top);
+    denom += ml[2 * w + 1] * fw[w];
+  }
+  const float inv = 1.0f / denom;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < PA_WARPS; ++w) o = fmaf(acc_s[w * dv + c], fw[w], o);
+    os[c] = o * inv;
+  }
+  __syncthreads();
+  TT* out = (TT*)A.out + t * A.ldo + (size_t)h * dv;
+  const float* gate = A.gates ? A.gates + t * A.ldgate + (size_t)h * dv : nullptr;
+  if (A.freq_v) {
+    const int half = dv / 2;
+    const float p = (float)i;
+    for (int c = threadIdx.x; c < half; c += blockDim.x) {
+      float cs, sn;
+      pa_sincos(p, A.freq_v, c, cs, sn);
+      const float a = os[c], b = os[c + half];
+      float x0 = a * cs + b * sn, x1 = b * cs - a * sn;        // turned by -p
+      if (gate) {
+        x0 *= 1.0f / (1.0f + expf(-gate[c]));
+        x1 *= 1.0f / (1.0f + expf(-gate[c + half]));
+      }
+      out[c] = co_from_float<TT>(x0);
+      out[c + half] = co_from_float<TT>(x1);
+    }
+  } else {
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+      float x = os[c];
+      if (gate) x *= 1.0f / (1.0f + expf(-gate[c]));
+      out[c] = co_from_float<TT>(x);
+    }
+  }
+}
+
+}  // namespace
+
+CO_EXPORT int coheryn_pooled_prepare(const float* proj, long ld, const int* positions, const float* freq_k, int rot,
+                                     const float* freq_v, void* q_out, long ldq, int dtype, const int* slots, void* k_cache,
+                                     void* v_cache, int T, int H, int G, int dk, int dv, int page_size, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rot < 0 || rot > dk || (rot & 1)) CO_FAIL("pooled_prepare: %d rotated channels of %d", rot, dk);
+  if (rot && !freq_k) CO_FAIL("pooled_prepare: a rotation needs frequencies");
+  if (freq_v && (dv & 1)) CO_FAIL("pooled_prepare: rotated values need an even number of channels, not %d", dv);
+  dim3 grid(T, H + (slots ? 2 * G : 0));
+  const int threads = 64;
+  if (dtype == CO_F32)
+    co_launch(pooled_prepare_kernel<float>, grid, dim3(threads), 0, stream, proj, ld, positions, freq_k, rot, freq_v, (float*)q_out, ldq,
+              slots, (float*)k_cache, (float*)v_cache, H, G, dk, dv, page_size);
+  else if (dtype == CO_BF16)
+    co_launch(pooled_prepare_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, proj, ld, positions, freq_k, rot, freq_v,
+              (__nv_bfloat16*)q_out, ldq, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, dk, dv, page_size);
+  else CO_FAIL("pooled_prepare: unknown dtype %d", dtype);
+  CO_CHECK_LAUNCH("pooled_prepare");
+  return 0;
+}
+
+CO_EXPORT int coheryn_pooled_means(const void* k_cache, const void* v_cache, void* pk_cache, void* pv_cache, int dtype,
+                                   const int* tables, int table_width, const int* pool_tables, int pool_table_width,
+                                   const int* cu_q, const int* kv_lens, int B, int max_q_len, int G, int dk, int dv, int page_size,
+                                   int pool, int pool_rows, cudaStream_t stream) {
+  if (B <= 0 || pool < 1) return 0;
+  if (pool_rows < (page_size + pool - 1) / pool) CO_FAIL("pooled_means: %d rows per page do not hold the blocks of a page", pool_rows);
+  const int per_request = max_q_len / pool + 1;
+  dim3 grid(B * per_request, G);
+#define GO(TT)                                                                                                               \
+  co_launch(pooled_means_kernel<TT>, grid, dim3(128), 0, stream, (const TT*)k_cache, (const TT*)v_cache, (TT*)pk_cache,        \
+            (TT*)pv_cache, tables, table_width, pool_tables, pool_table_width, cu_q, kv_lens, per_request, G, dk, dv, page_size, \
+            pool, pool_rows)
+  if (dtype == CO_F32) GO(float);
+  else if (dtype == CO_BF16) GO(__nv_bfloat16);
+  else CO_FAIL("pooled_means: unknown dtype %d", dtype);
+#undef GO
+  CO_CHECK_LAUNCH("pooled_means");
+  return 0;
+}
+
+CO_EXPORT int coheryn_pooled_attention(const void* q, long ldq, void* out, long ldo, const void* k, const void* v, const void* pk,
+                                       const void* pv, int dtype, const int* tables, int table_width, const int* pool_tables,
+                                       int pool_table_width, const int* token_req, const int* positions, const float* temps,
+                                       const float* sinks, const float* gates, long ldgate, const float* freq_v, int T, int H, int G,
+                                       int dk, int dv, int page_size, int window, int pool, int pool_rows, float scale, float cap,
+                                       cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H < 1 || G < 1 || H % G) CO_FAIL("pooled_attention: %d heads over %d key heads", H, G);
+  if (dk < 1 || dk > 32 * PA_MAX_PER_LANE || dv < 1 || dv > 32 * PA_MAX_PER_LANE)
+    CO_FAIL("pooled_attention: head sizes %d / %d (1..%d)", dk, dv, 32 * PA_MAX_PER_LANE);
+  if (pool > 0 && (!pk || !pv || !pool_tables)) CO_FAIL("pooled_attention: blocks need their cache");
+  AttnArgs A{q, ldq, out, ldo, k, v, pk, pv, tables, table_width, pool_tables, pool_table_width, token_req, positions, temps, sinks,
+             gates, ldgate, freq_v, H, G, dk, dv, page_size, window, pool, pool_rows, scale, cap};
+  const size_t smem = (size_t)(dk + (PA_WARPS + 1) * dv + 2 * PA_WARPS) * sizeof(float);
+  if (dtype == CO_F32) co_launch(pooled_attention_kernel<float>, dim3(T, H), dim3(PA_WARPS * 32), smem, stream, A);
+  else if (dtype == CO_BF16) co_launch(pooled_attention_kernel<__nv_bfloat16>, dim3(T, H), dim3(PA_WARPS * 32), smem, stream, A);
+  else CO_FAIL("pooled_attention: unknown dtype %d", dtype);
+  CO_CHECK_LAUNCH("pooled_attention");
+  return 0;
+}

@@ -34,6 +34,8 @@ CORE_SOURCES = ["runtime.cu", "elementwise.cu", "gemm_simt.cu", "attention_simpl
 ROUTED_SOURCES = ["routed.cu", "runtime.cu"]
 RECURRENT_SOURCES = ["recurrent.cu", "runtime.cu"]
 VARIANT_SOURCES = ["attention_variants.cu", "runtime.cu"]
+LINEAR_RECURRENCE_SOURCES = ["linear_recurrence.cu", "runtime.cu"]
+POOLED_ATTENTION_SOURCES = ["attention_pooled.cu", "runtime.cu"]
 HEADERS = ["common.cuh"]
 
 
@@ -249,6 +251,18 @@ def variants_library() -> ctypes.CDLL:
     return load_library("variants", VARIANT_SOURCES)
 
 
+def linear_recurrence_library() -> ctypes.CDLL:
+    """The kernels of mixers whose state is one number per channel: a short convolution with a bias and the gated scan.
+    Compiled when a model with such a mixer is first run."""
+    return load_library("linear_recurrence", LINEAR_RECURRENCE_SOURCES)
+
+
+def pooled_attention_library() -> ctypes.CDLL:
+    """Window attention over positions and block means (float32 arithmetic) with the kernels that rotate and write its
+    keys and values and keep the block means.  Compiled when a model with such a mixer is first run."""
+    return load_library("pooled_attention", POOLED_ATTENTION_SOURCES)
+
+
 def routed_library() -> ctypes.CDLL:
     """Routing of tokens to experts and matrix products over groups of rows that each meet a matrix of their own (experts,
     or the heads of an attention with a matrix per head).  Compiled when a model with such a part is first run."""
@@ -274,7 +288,9 @@ def maps_attention_library(dk: int, dv: int, maps: int, values_in_keys: bool = F
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     """Compile everything ahead of time (no GPU needed)."""
     paths = [build_host_library(), build_library("core", CORE_SOURCES), build_library("recurrent", RECURRENT_SOURCES),
-             build_library("variants", VARIANT_SOURCES), build_library("routed", ROUTED_SOURCES)]
+             build_library("variants", VARIANT_SOURCES), build_library("routed", ROUTED_SOURCES),
+             build_library("linear_recurrence", LINEAR_RECURRENCE_SOURCES),
+             build_library("pooled_attention", POOLED_ATTENTION_SOURCES)]
     paths.append(build_library("maps_96_64_1_vk", ["attention_maps_tc.cu", "runtime.cu"],
                                {"CO_MAPS_DK": 96, "CO_MAPS_DV": 64, "CO_MAPS_N": 1, "CO_MAPS_V_IN_K": 1}))
     for dk, dv, maps in ((64, 128, 2), (64, 64, 1)):

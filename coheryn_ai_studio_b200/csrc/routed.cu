@@ -27,7 +27,7 @@ constexpr int RS_WARPS = 4;
 // smem per warp: choice[N], prob[N], gbest[n_groups]
 __global__ void __launch_bounds__(RS_WARPS * 32)
 route_select_kernel(const float* __restrict__ logits, long ld, const void* __restrict__ correction, int c_dtype, int T, int N,
-                    int n_groups, int keep, int top, float scale, int* __restrict__ ids, float* __restrict__ weights) {
+                    int n_groups, int keep, int top, float scale, int mode, int* __restrict__ ids, float* __restrict__ weights) {
   extern __shared__ __align__(16) float sm[];
   co_pdl_launch_dependents();
   co_pdl_wait();
@@ -38,20 +38,25 @@ route_select_kernel(const float* __restrict__ logits, long ld, const void* __res
   float* prob = choice + N;
   float* gbest = prob + N;
   const float* z = logits + (size_t)t * ld;
-  float m = -INFINITY;
-  for (int i = lane; i < N; i += 32) m = fmaxf(m, z[i]);
-  m = co_warp_max(m);
-  float sum = 0.f;
-  for (int i = lane; i < N; i += 32) {
-    const float e = expf(z[i] - m);
-    prob[i] = e;
-    sum += e;
-  }
-  sum = co_warp_sum(sum);
-  for (int i = lane; i < N; i += 32) {
-    const float p = prob[i] / sum;
-    prob[i] = p;
-    choice[i] = p + (correction ? co_load_any(correction, c_dtype, i) : 0.f);
+  if (mode == 1) {
+    // the choice scores are the logits themselves (plus a bias); the weights come from the chosen ones alone
+    for (int i = lane; i < N; i += 32) choice[i] = z[i] + (correction ? co_load_any(correction, c_dtype, i) : 0.f);
+  } else {
+    float m = -INFINITY;
+    for (int i = lane; i < N; i += 32) m = fmaxf(m, z[i]);
+    m = co_warp_max(m);
+    float sum = 0.f;
+    for (int i = lane; i < N; i += 32) {
+      const float e = expf(z[i] - m);
+      prob[i] = e;
+      sum += e;
+    }
+    sum = co_warp_sum(sum);
+    for (int i = lane; i < N; i += 32) {
+      const float p = prob[i] / sum;
+      prob[i] = p;
+      choice[i] = p + (correction ? co_load_any(correction, c_dtype, i) : 0.f);
+    }
   }
   __syncwarp();
   if (n_groups > 1 && keep < n_groups) {
@@ -84,7 +89,7 @@ route_select_kernel(const float* __restrict__ logits, long ld, const void* __res
     __syncwarp();
   }
   // the `top` best choice scores, ties to the lower index; a chosen one is marked by NaN
-  float wsum = 0.f;
+  float wsum = 0.f, first = 0.f;
   for (int r = 0; r < top; ++r) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -99,7 +104,8 @@ route_select_kernel(const float* __restrict__ logits, long ld, const void* __res
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     // bi is valid while fewer experts are marked than may be chosen (top <= allowed experts, checked on the host)
-    const float p = prob[bi];
+    if (r == 0) first = bv;
+    const float p = mode == 1 ? expf(bv - first) : prob[bi];      // mode 1: softmax over the chosen logits, the largest first
     wsum += p;
     if (lane == 0) {
       ids[(size_t)t * top + r] = bi;
@@ -378,13 +384,15 @@ template <typename TH>
 __global__ void __launch_bounds__(256)
 route_combine_kernel(const float* __restrict__ y, long ldy, const TH* __restrict__ h, long ldh, const int* __restrict__ ids,
                      const float* __restrict__ weights, const int* __restrict__ row_of, int top, int E, float* __restrict__ out,
-                     int H) {
+                     int H, const float* __restrict__ extra, long ld_extra, const float* __restrict__ extra_gate, long ld_gate) {
   constexpr int KEEP = 64;                    // choices whose rows and weights are looked up once, into shared memory
   __shared__ int row_s[KEEP];
   __shared__ float w_s[KEEP];
   co_pdl_launch_dependents();
   co_pdl_wait();
   const size_t t = blockIdx.x;
+  // one more summand per token, added last: extra[t] times sigmoid(extra_gate[t]) (or times 1 without a gate)
+  const float xw = !extra ? 0.f : extra_gate ? 1.0f / (1.0f + expf(-extra_gate[t * ld_gate])) : 1.f;
   if (top <= KEEP) {
     if ((int)threadIdx.x < top) {
       const int e = ids[t * top + threadIdx.x];
@@ -392,7 +400,8 @@ route_combine_kernel(const float* __restrict__ y, long ldy, const TH* __restrict
       w_s[threadIdx.x] = weights[t * top + threadIdx.x];
     }
     __syncthreads();
-    const bool wide = (H & 3) == 0 && (ldy & 3) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    const bool wide = (H & 3) == 0 && (ldy & 3) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                      (!extra || ((ld_extra & 3) == 0 && ((uintptr_t)extra & 15) == 0));
     if (wide) {          // four columns a thread, the rows of all choices requested before any is used
       for (int j = 4 * threadIdx.x; j < H; j += 4 * blockDim.x) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -405,6 +414,10 @@ route_combine_kernel(const float* __restrict__ y, long ldy, const TH* __restrict
           const float w = w_s[k];
           acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
         }
+        if (extra) {
+          const float4 x = *reinterpret_cast<const float4*>(extra + t * ld_extra + j);
+          acc.x = fmaf(xw, x.x, acc.x); acc.y = fmaf(xw, x.y, acc.y); acc.z = fmaf(xw, x.z, acc.z); acc.w = fmaf(xw, x.w, acc.w);
+        }
         *reinterpret_cast<float4*>(out + t * H + j) = acc;
       }
       return;
@@ -415,7 +428,7 @@ route_combine_kernel(const float* __restrict__ y, long ldy, const TH* __restrict
         const int r = row_s[k];
         acc = fmaf(w_s[k], r >= 0 ? y[(size_t)r * ldy + j] : co_to_float(h[t * ldh + j]), acc);
       }
-      out[t * H + j] = acc;
+      out[t * H + j] = extra ? fmaf(xw, extra[t * ld_extra + j], acc) : acc;
     }
     return;
   }
@@ -427,16 +440,17 @@ route_combine_kernel(const float* __restrict__ y, long ldy, const TH* __restrict
       const float v = e < E ? y[(size_t)row_of[t * top + k] * ldy + j] : co_to_float(h[t * ldh + j]);
       acc = fmaf(w, v, acc);
     }
-    out[t * H + j] = acc;
+    out[t * H + j] = extra ? fmaf(xw, extra[t * ld_extra + j], acc) : acc;
   }
 }
 
 }  // namespace
 
 CO_EXPORT int coheryn_route_select(const float* logits, long ld, const void* correction, int c_dtype, int T, int N, int n_groups,
-                                   int keep, int top, float scale, int* ids, float* weights, cudaStream_t stream) {
+                                   int keep, int top, float scale, int mode, int* ids, float* weights, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (N < 1 || top < 1 || top > N) CO_FAIL("route_select: %d choices among %d outputs", top, N);
+  if (mode != 0 && mode != 1) CO_FAIL("route_select: unknown mode %d", mode);
   if (n_groups < 1) n_groups = 1;
   if (N % n_groups) CO_FAIL("route_select: %d outputs do not form %d equal groups", N, n_groups);
   if (keep < 1 || keep > n_groups) keep = n_groups;
@@ -445,7 +459,7 @@ CO_EXPORT int coheryn_route_select(const float* logits, long ld, const void* cor
   if (smem > 200 * 1024) CO_FAIL("route_select: %d outputs do not fit in shared memory", N);
   if (smem > 48 * 1024) cudaFuncSetAttribute(route_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   co_launch(route_select_kernel, dim3((T + RS_WARPS - 1) / RS_WARPS), dim3(RS_WARPS * 32), smem, stream, logits, ld, correction,
-            c_dtype, T, N, n_groups, keep, top, scale, ids, weights);
+            c_dtype, T, N, n_groups, keep, top, scale, mode, ids, weights);
   CO_CHECK_LAUNCH("route_select");
   return 0;
 }
@@ -515,12 +529,12 @@ CO_EXPORT int coheryn_grouped_linear(const void* A, int a_dtype, long lda, long 
 // y float32 [rows, H] (row stride ldy): the experts' outputs in sorted order; h [T, H]: the tokens' inputs (identity experts).
 CO_EXPORT int coheryn_route_combine(const float* y, long ldy, const void* h, int h_dtype, long ldh, const int* ids,
                                     const float* weights, const int* row_of, int top, int E, float* out, int T, int H,
-                                    cudaStream_t stream) {
+                                    const float* extra, long ld_extra, const float* extra_gate, long ld_gate, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (h_dtype == CO_F32)
-    co_launch(route_combine_kernel<float>, dim3(T), dim3(256), 0, stream, y, ldy, (const float*)h, ldh, ids, weights, row_of, top, E, out, H);
+    co_launch(route_combine_kernel<float>, dim3(T), dim3(256), 0, stream, y, ldy, (const float*)h, ldh, ids, weights, row_of, top, E, out, H, extra, ld_extra, extra_gate, ld_gate);
   else if (h_dtype == CO_BF16)
-    co_launch(route_combine_kernel<bf16>, dim3(T), dim3(256), 0, stream, y, ldy, (const bf16*)h, ldh, ids, weights, row_of, top, E, out, H);
+    co_launch(route_combine_kernel<bf16>, dim3(T), dim3(256), 0, stream, y, ldy, (const bf16*)h, ldh, ids, weights, row_of, top, E, out, H, extra, ld_extra, extra_gate, ld_gate);
   else CO_FAIL("route_combine: unknown dtype %d", h_dtype);
   CO_CHECK_LAUNCH("route_combine");
   return 0;

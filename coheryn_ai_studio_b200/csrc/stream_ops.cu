@@ -321,3 +321,47 @@ CO_EXPORT int coheryn_gated_table_mul(const void* z, int z_dtype, long ldz, cons
   CO_CHECK_LAUNCH("gated_table_mul");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// The input of a product that mixes the stream with the embedding output: row t of `out` [T, 2 H] (compute dtype) is
+// [x[t] + the pending summands | table[id[t]] * scale].  The stream itself is not changed (the product's result replaces
+// it).  parts: P float32 stacks of [T, H] (part_stride apart) or null; delta16: one pending summand in bfloat16, or null.
+// ---------------------------------------------------------------------------------
+namespace {
+template <typename TW, typename TO>
+__global__ void stream_join_kernel(const float* __restrict__ x, const float* __restrict__ parts, int P, long part_stride,
+                                   const __nv_bfloat16* __restrict__ delta16, const TW* __restrict__ table,
+                                   const int* __restrict__ ids, float scale, TO* __restrict__ out, int H, int V) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  const int id = ids[t];
+  const TW* row = (id >= 0 && id < V) ? table + (size_t)id * H : nullptr;    // the embedding kernel has flagged such an id
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float v = x[t * H + j];
+    for (int p = 0; p < P; ++p) v += parts[(size_t)p * part_stride + t * H + j];
+    if (delta16) v += __bfloat162float(delta16[t * H + j]);
+    out[t * 2 * H + j] = co_from_float<TO>(v);
+    out[t * 2 * H + H + j] = co_from_float<TO>(row ? co_to_float(row[j]) * scale : 0.f);
+  }
+}
+}  // namespace
+
+CO_EXPORT int coheryn_stream_join(const float* x, const float* parts, int P, long part_stride, const void* delta16,
+                                  const void* table, int table_dtype, const int* ids, float scale, void* out, int out_dtype,
+                                  int T, int H, int V, cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  const __nv_bfloat16* d16 = (const __nv_bfloat16*)delta16;
+#define GO(TW, TO)                                                                                                     \
+  co_launch(stream_join_kernel<TW, TO>, dim3(T), dim3(threads), 0, stream, x, parts, P, part_stride, d16, (const TW*)table, \
+            ids, scale, (TO*)out, H, V)
+  if (table_dtype == CO_F32 && out_dtype == CO_F32) GO(float, float);
+  else if (table_dtype == CO_BF16 && out_dtype == CO_BF16) GO(__nv_bfloat16, __nv_bfloat16);
+  else if (table_dtype == CO_F32 && out_dtype == CO_BF16) GO(float, __nv_bfloat16);
+  else if (table_dtype == CO_BF16 && out_dtype == CO_F32) GO(__nv_bfloat16, float);
+  else CO_FAIL("stream_join: unknown dtypes %d / %d", table_dtype, out_dtype);
+#undef GO
+  CO_CHECK_LAUNCH("stream_join");
+  return 0;
+}

@@ -183,6 +183,31 @@ def stream_inject(x: torch.Tensor, table: Optional[torch.Tensor], ids: Optional[
                                           _stream()))
 
 
+def stream_join(x: torch.Tensor, delta: Optional[torch.Tensor], table: torch.Tensor, ids: torch.Tensor,
+                scale: Optional[float], dtype: torch.dtype) -> torch.Tensor:
+    """[x + pending summands | table[ids] * scale] as [T, 2 H] in ``dtype``: the input of a product that mixes the stream
+    with the embedding output.  ``delta``: None, a float32 [T, H] or stack [P, T, H], or a bfloat16 [T, H]."""
+    _dev(x, delta, table, ids)
+    _i32(ids, "ids")
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous() and table.shape[1] == H
+    parts, P, stride, d16 = None, 0, 0, None
+    if delta is not None:
+        assert delta.is_contiguous() and tuple(delta.shape[-2:]) == (T, H)
+        if delta.dtype == torch.float32:
+            parts, P, stride = delta, (delta.shape[0] if delta.dim() == 3 else 1), T * H
+        elif delta.dtype == torch.bfloat16 and delta.dim() == 2:
+            d16 = delta
+        else:
+            raise KernelError("stream_join: a pending summand is float32 (one or a stack) or one bfloat16 tensor")
+    out = torch.empty((T, 2 * H), dtype=dtype, device=x.device)
+    lib = core()
+    _check(lib, lib.coheryn_stream_join(_ptr(x), _ptr(parts), c_int(P), c_long(stride), _ptr(d16), _ptr(table),
+                                        c_int(_code(table)), _ptr(ids), c_float(1.0 if scale is None else scale), _ptr(out),
+                                        c_int(_CODES[dtype]), c_int(T), c_int(H), c_int(table.shape[0]), _stream()))
+    return out
+
+
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None, update: bool = True) -> None:
     """x = resid (+ delta); resid = x if update; out = x / sqrt(mean(x^2) + eps) * weight.
@@ -1368,10 +1393,11 @@ def set_grouped_tc(on: bool) -> None:
 
 
 def route_select(logits: torch.Tensor, correction: Optional[torch.Tensor], n_groups: int, keep: int, top: int,
-                 scale: float):
+                 scale: float, chosen_softmax: bool = False):
     """From router logits (float32 [T, N]) the chosen outputs per token (int32 [T, top], by choice score = softmax +
     correction, only within the ``keep`` best of ``n_groups`` equal groups of neighbours) and their weights (float32
-    [T, top]: the chosen probabilities over their sum, times ``scale``)."""
+    [T, top]: the chosen probabilities over their sum, times ``scale``).  ``chosen_softmax``: the choice scores are the
+    logits themselves plus ``correction`` (a bias), and the weights the softmax over the chosen scores alone."""
     _dev(logits, correction)
     _f32(logits, "logits")
     T, N = logits.shape
@@ -1383,8 +1409,8 @@ def route_select(logits: torch.Tensor, correction: Optional[torch.Tensor], n_gro
     lib = routed()
     _check(lib, lib.coheryn_route_select(_ptr(logits), c_long(logits.stride(0)), _ptr(correction),
                                          c_int(_code(correction) if correction is not None else F32), c_int(T), c_int(N),
-                                         c_int(n_groups), c_int(keep), c_int(top), c_float(scale), _ptr(ids), _ptr(weights),
-                                         _stream()))
+                                         c_int(n_groups), c_int(keep), c_int(top), c_float(scale),
+                                         c_int(1 if chosen_softmax else 0), _ptr(ids), _ptr(weights), _stream()))
     return ids, weights
 
 
@@ -1477,10 +1503,16 @@ def grouped_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: Op
 
 
 def route_combine(y: torch.Tensor, h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, rows: RoutedRows,
-                  out: torch.Tensor) -> None:
+                  out: torch.Tensor, extra: Optional[torch.Tensor] = None, extra_gate: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum over the token's choices in order of weight * (y[row of the pair] for an expert, h[t] for an
-    identity output); y float32 in sorted order, out float32 [T, H]."""
-    _dev(y, h, ids, weights, out)
+    identity output); y float32 in sorted order, out float32 [T, H].  ``extra`` (float32 [T, H]) is one more summand,
+    added last, multiplied by sigmoid(extra_gate[t]) when ``extra_gate`` (float32 [T], may be a strided column) is given."""
+    _dev(y, h, ids, weights, out, extra, extra_gate)
+    if extra is not None:
+        _f32(extra, "extra")
+        assert extra.shape == out.shape and extra.stride(1) == 1
+    if extra_gate is not None:
+        assert extra is not None and extra_gate.dtype == torch.float32 and extra_gate.shape == (out.shape[0],)
     _f32(y, "y"); _f32(out, "out")
     T, top = ids.shape
     H = out.shape[1]
@@ -1488,7 +1520,9 @@ def route_combine(y: torch.Tensor, h: torch.Tensor, ids: torch.Tensor, weights: 
     lib = routed()
     _check(lib, lib.coheryn_route_combine(_ptr(y), c_long(y.stride(0)), _ptr(h), c_int(_code(h)), c_long(h.stride(0)), _ptr(ids),
                                           _ptr(weights), _ptr(rows.row_of), c_int(top), c_int(rows.experts), _ptr(out), c_int(T),
-                                          c_int(H), _stream()))
+                                          c_int(H), _ptr(extra), c_long(extra.stride(0) if extra is not None else 0),
+                                          _ptr(extra_gate), c_long(extra_gate.stride(0) if extra_gate is not None else 0),
+                                          _stream()))
 
 
 def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rd: int, rank: int, kv_col: Optional[int],
@@ -1523,3 +1557,162 @@ def latent_prepare(proj: torch.Tensor, heads: int, dim: int, rd: int, rank: int,
         _ptr(cache) if write else c_void_p(0), c_int(T), c_int(heads), c_int(dim), c_int(rd), c_int(rank), c_int(page_size),
         _stream()))
     return q_plain, q_wide
+
+
+# ------------------------------------------------------------------------------------
+# A gated linear recurrence per channel (csrc/linear_recurrence.cu, a library of its own that is compiled when a model
+# with such a mixer is first run).
+_linear_recurrence = None
+
+
+def linear_recurrence():
+    global _linear_recurrence
+    if _linear_recurrence is None:
+        lib = build.linear_recurrence_library()
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        lib.coheryn_gated_scan_scratch.restype = ctypes.c_long
+        _linear_recurrence = lib
+    return _linear_recurrence
+
+
+def conv_bias(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, step,
+              update_state: bool = True) -> torch.Tensor:
+    """y[t, c] = bias[c] + sum_j taps[c, j] * x[t - (n-1) + j, c] over each request's run of tokens, no activation; inputs
+    before the step's first token come from ``state`` (a float32 view [slots, (n-1) * C] whose rows may be strided), which
+    then receives the last n-1 inputs.  ``x`` float32 [T, C] (a column slice is fine); returns float32 [T, C]."""
+    _dev(x, taps, bias, state, step.token_req, step.cu_q, step.state_slots)
+    _f32(x, "x"); _f32(state, "state")
+    T, C = x.shape
+    n = taps.shape[1]
+    assert taps.shape == (C, n) and taps.is_contiguous() and state.shape[1] == (n - 1) * C
+    if bias is not None:
+        assert bias.shape == (C,) and bias.is_contiguous()
+    y = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    lib = linear_recurrence()
+    _check(lib, lib.coheryn_conv_bias(
+        _ptr(x), c_long(x.stride(0)), _ptr(y), c_long(y.stride(0)), _ptr(taps), c_int(_code(taps)), _ptr(bias),
+        c_int(_code(bias) if bias is not None else F32), c_int(n), c_int(C), _ptr(state), c_long(state.stride(0)),
+        _ptr(step.token_req), _ptr(step.cu_q), _ptr(step.state_slots), c_int(T), c_int(step.num_requests),
+        c_int(1 if update_state else 0), _stream()))
+    return y
+
+
+def gated_scan(gates: torch.Tensor, bias_r: Optional[torch.Tensor], bias_i: Optional[torch.Tensor], u: torch.Tensor,
+               y: torch.Tensor, lam: torch.Tensor, rate: float, block: int, state: torch.Tensor, step,
+               out: torch.Tensor) -> None:
+    """S_t = a S_(t-1) + sqrt(1 - a^2) * i * u per channel and request, a = exp(-rate * r * softplus(lam)), r and i the
+    sigmoids of the gates' pre-activations (+ biases); out_t = S_t * gelu_tanh(y_t).  ``gates`` float32 [T, 2 C]: per block
+    of ``block`` channels [r | i]; ``u``, ``y`` float32 [T, C]; ``state`` float32 [slots, C] (rows may be strided), read at a
+    request's first token of the step and written at its last; ``out`` [T, C] float32 or bfloat16."""
+    _dev(gates, bias_r, bias_i, u, y, lam, state, out, step.token_req, step.cu_q, step.state_slots)
+    _f32(gates, "gates"); _f32(u, "u"); _f32(y, "y"); _f32(state, "state")
+    T, C = u.shape
+    assert gates.shape == (T, 2 * C) and y.shape == (T, C) and out.shape == (T, C) and out.stride(1) == 1
+    assert lam.shape == (C,) and lam.is_contiguous() and state.shape[1] == C
+    if bias_r is not None:
+        assert bias_i is not None and bias_r.dtype == bias_i.dtype and bias_r.numel() == C and bias_i.numel() == C
+        assert bias_r.is_contiguous() and bias_i.is_contiguous()
+    lib = linear_recurrence()
+    B = step.num_requests
+    floats = int(lib.coheryn_gated_scan_scratch(c_int(T), c_int(B), c_int(C)))
+    scratch = torch.empty(floats, dtype=torch.float32, device=u.device)
+    _check(lib, lib.coheryn_gated_scan(
+        _ptr(gates), c_long(gates.stride(0)), _ptr(bias_r), _ptr(bias_i), c_int(_code(bias_r) if bias_r is not None else F32),
+        _ptr(u), c_long(u.stride(0)), _ptr(y), c_long(y.stride(0)), _ptr(lam), c_int(_code(lam)), c_float(rate), c_int(block),
+        _ptr(state), c_long(state.stride(0)), _ptr(step.token_req), _ptr(step.cu_q), _ptr(step.state_slots), _ptr(scratch),
+        c_long(floats), _ptr(out), c_int(_code(out)), c_long(out.stride(0)), c_int(T), c_int(B), c_int(C), _stream()))
+
+
+# ------------------------------------------------------------------------------------
+# Window attention over positions and block means (csrc/attention_pooled.cu, a library of its own that is compiled when
+# a model with such a mixer is first run).
+_pooled = None
+
+
+def pooled():
+    global _pooled
+    if _pooled is None:
+        lib = build.pooled_attention_library()
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        _pooled = lib
+    return _pooled
+
+
+def pooled_prepare(proj: torch.Tensor, positions: torch.Tensor, freq_k: Optional[torch.Tensor], rot: int,
+                   freq_v: Optional[torch.Tensor], slots: Optional[torch.Tensor], k_cache, v_cache, heads: int, kv_heads: int,
+                   dk: int, dv: int, page_size: int, dtype: torch.dtype) -> torch.Tensor:
+    """``proj`` float32 [T, >= heads * dk + kv_heads * (dk + dv)]: queries, keys, values side by side.  The first ``rot``
+    channels of every query and key head are rotated by the row's position (``freq_k`` float32 [rot/2, 2], high and low
+    part of each pair's frequency), all ``dv`` channels of every value head by ``freq_v`` ([dv/2, 2]; None: values stay as
+    they are); keys and values go to the cache at ``slots`` (None: only queries are made).  Returns q [T, heads * dk]."""
+    _dev(proj, positions, freq_k, freq_v, slots, k_cache, v_cache)
+    _f32(proj, "proj"); _i32(positions, "positions")
+    T = proj.shape[0]
+    assert proj.shape[1] >= heads * dk + (kv_heads * (dk + dv) if slots is not None else 0)
+    for f, n in ((freq_k, rot), (freq_v, dv)):
+        if f is not None:
+            assert f.dtype == torch.float32 and f.is_contiguous() and tuple(f.shape) == (n // 2, 2)
+    if slots is not None:
+        _i32(slots, "slots")
+        assert k_cache.dtype == dtype and v_cache.dtype == dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (kv_heads, page_size, dk) and tuple(v_cache.shape[1:]) == (kv_heads, page_size, dv)
+    q = torch.empty((T, heads * dk), dtype=dtype, device=proj.device)
+    lib = pooled()
+    _check(lib, lib.coheryn_pooled_prepare(
+        _ptr(proj), c_long(proj.stride(0)), _ptr(positions), _ptr(freq_k), c_int(rot if freq_k is not None else 0), _ptr(freq_v),
+        _ptr(q), c_long(q.stride(0)), c_int(_CODES[dtype]), _ptr(slots), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(heads),
+        c_int(kv_heads), c_int(dk), c_int(dv), c_int(page_size), _stream()))
+    return q
+
+
+def pooled_means(k_cache, v_cache, pk_cache, pv_cache, step, group: int, pool_group: int, kv_heads: int, dk: int, dv: int,
+                 page_size: int, pool: int) -> None:
+    """For every block of ``pool`` positions whose last position the step wrote: the mean of its keys and of its values
+    (read from the cache, added in position order, float32) into the block cache, whose pages ([page, kv head, rows,
+    channels], rows = ceil(page_size / pool)) hang on the block table of ``pool_group``."""
+    tables, ptables = step.block_tables[group], step.block_tables[pool_group]
+    _dev(k_cache, v_cache, pk_cache, pv_cache, tables, ptables, step.cu_q, step.kv_lens)
+    rows = pk_cache.shape[2]
+    assert pk_cache.dtype == k_cache.dtype and tuple(pk_cache.shape[1:]) == (kv_heads, rows, dk)
+    assert tuple(pv_cache.shape[1:]) == (kv_heads, rows, dv) and pk_cache.is_contiguous() and pv_cache.is_contiguous()
+    lib = pooled()
+    _check(lib, lib.coheryn_pooled_means(
+        _ptr(k_cache), _ptr(v_cache), _ptr(pk_cache), _ptr(pv_cache), c_int(_code(k_cache)), _ptr(tables), c_int(tables.shape[1]),
+        _ptr(ptables), c_int(ptables.shape[1]), _ptr(step.cu_q), _ptr(step.kv_lens), c_int(step.num_requests),
+        c_int(max(int(step.max_q_len), 1)), c_int(kv_heads), c_int(dk), c_int(dv), c_int(page_size), c_int(pool), c_int(rows),
+        _stream()))
+
+
+def pooled_attention(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, pk_cache, pv_cache, step, group: int,
+                     pool_group: Optional[int], heads: int, kv_heads: int, dk: int, dv: int, page_size: int,
+                     window: Optional[int], pool: Optional[int], scale: float, softcap: Optional[float],
+                     temps: Optional[torch.Tensor], sinks: Optional[torch.Tensor], gates: Optional[torch.Tensor],
+                     freq_v: Optional[torch.Tensor]) -> None:
+    """Attention of every row of the step over the last ``window`` positions of its request and the means of the blocks
+    of ``pool`` positions that lie wholly before them (see csrc/attention_pooled.cu).  q [T, heads * dk], out
+    [T, heads * dv] in the caches' dtype; ``temps``, ``sinks`` float32 [heads]; ``gates`` float32 [T, heads * dv] (rows may
+    be strided): the output passes sigmoid(gates); ``freq_v``: the values were rotated, the output is turned back."""
+    tables = step.block_tables[group]
+    ptables = step.block_tables[pool_group] if pool else None
+    _dev(q, out, k_cache, v_cache, pk_cache, pv_cache, tables, ptables, step.token_req, step.positions, temps, sinks, gates, freq_v)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == heads * dk and out.shape == (T, heads * dv)
+    assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype
+    for v in (temps, sinks):
+        if v is not None:
+            assert v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads
+    if gates is not None:
+        _f32(gates, "gates")
+        assert gates.shape == (T, heads * dv)
+    if pool and not window:
+        raise KernelError("pooled_attention: block means stand for positions before a window; without a window there are none")
+    lib = pooled()
+    _check(lib, lib.coheryn_pooled_attention(
+        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(pk_cache),
+        _ptr(pv_cache), c_int(_code(q)), _ptr(tables), c_int(tables.shape[1]), _ptr(ptables),
+        c_int(ptables.shape[1] if ptables is not None else 0), _ptr(step.token_req), _ptr(step.positions), _ptr(temps), _ptr(sinks),
+        _ptr(gates), c_long(gates.stride(0) if gates is not None else 0), _ptr(freq_v), c_int(T), c_int(heads), c_int(kv_heads),
+        c_int(dk), c_int(dv), c_int(page_size), c_int(window or 0), c_int(pool or 0),
+        c_int(pk_cache.shape[2] if pool else 0), c_float(scale), c_float(softcap or 0.0), _stream()))

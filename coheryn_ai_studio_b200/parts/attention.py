@@ -15,6 +15,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import ops
+from ..config.spec import PartSpec
 from ..weights.spec import TensorSpec
 from .base import LayerCache, Mixer, PagedKV, Position, Runtime, StepContext, register_mixer
 
@@ -561,6 +562,143 @@ class LatentAttention(Mixer):
         return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
 
 
+class PooledWindowAttention(Mixer):
+    """Grouped-query attention over a sliding window whose older keys are seen as block means.
+
+    Position i sees the positions j with 0 <= i - j < ``window`` and, beside them, ONE key and value for each block of
+    ``pool`` consecutive positions that lies wholly before the window: block b (positions b pool .. b pool + pool - 1)
+    is seen when b pool + pool - 1 <= i - window; its key is the mean of the block's keys as the cache holds them
+    (rotated), its value the mean of the values.  Positions that have left the window and whose block is not complete
+    behind it are not seen.  Positions and blocks share one softmax.  ``pool`` None: a plain window; ``window`` None:
+    every earlier position.  Options, each independent of the others:
+
+    * ``qkv_bias``: biases on the three projections (tensors ``q.b``, ``k.b``, ``v.b``);
+    * ``position``: the first ``rotary_dim`` channels of every query and key head turn by the position (pairs
+      (i, i + rotary_dim / 2), angles computed from the frequencies);
+    * ``rotate_values``: the value of position j turns by j over ALL its channels (pairs (m, m + vdim / 2), pair m by
+      j base^(-2m / vdim), ``value_base`` being the base) and is cached so; a head's output at position i is turned
+      back by -i, so a value enters with the angle of its distance;
+    * ``head_temps``: the score (q . k) ``scale`` is multiplied by a learned number per head (tensor ``temp``);
+    * ``softcap``: score <- cap tanh(score / cap);
+    * ``sink``: the softmax's denominator has one more term exp(sink_h), a learned number per head (tensor ``sink``)
+      without key or value, neither scaled nor capped;
+    * ``gate``: the concatenated heads are multiplied by sigmoid(W_g x) (tensor ``g``), x being the mixer's input.
+
+    The cache is two sets of pages: keys and values of every position, and one row per block (``PagedKV.stride``) that
+    the step which completes a block fills from the cached rows."""
+
+    output_parts = 1
+
+    def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 v_head_dim: Optional[int], scale: float, window: Optional[int] = None, pool: Optional[int] = None,
+                 qkv_bias: bool = False, rotate_values: bool = False, value_base: Optional[float] = None,
+                 head_temps: bool = False, softcap: Optional[float] = None, sink: bool = False, gate: bool = False,
+                 float32_output: bool = True, position: Optional[Position] = None):
+        super().__init__(runtime)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} kv heads")
+        for name, v in (("window", window), ("pool", pool)):
+            if v is not None and v < 1:
+                raise ValueError(f"an attention {name} must hold at least one position")
+        if pool is not None and window is None:
+            raise ValueError("block means stand for the positions before a window; without a window there are none")
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv = int(head_dim), int(v_head_dim if v_head_dim is not None else head_dim)
+        self.scale, self.window, self.pool = float(scale), window, pool
+        self.qkv_bias, self.head_temps, self.sink, self.gate = bool(qkv_bias), bool(head_temps), bool(sink), bool(gate)
+        self.softcap = float(softcap) if softcap else None
+        self.position = position
+        if position is not None and position.rotary_dim > self.dk:
+            raise ValueError(f"{position.rotary_dim} rotated channels do not fit a head of {self.dk}")
+        self.value_position = None
+        if rotate_values:
+            if self.dv % 2:
+                raise ValueError("rotated values need an even number of channels")
+            base = value_base if value_base is not None else getattr(position, "theta", None)
+            if base is None:
+                raise ValueError("rotated values need the base of their frequencies")
+            from .base import POSITIONS, build_part
+            self.value_position = build_part(POSITIONS, "position", PartSpec("rope_computed", dict(rotary_dim=self.dv, theta=float(base))), runtime)
+        self.out_dtype = torch.float32 if float32_output else None
+        self.w_in = self.b_in = self.w_o = self.temps = self.sinks = None
+
+    def cache_requirement(self):
+        kv = PagedKV(self.num_kv_heads, self.dk, None, None if self.dv == self.dk else self.dv)
+        if self.pool is None:
+            return kv
+        return (kv, PagedKV(self.num_kv_heads, self.dk, None, None if self.dv == self.dk else self.dv, stride=self.pool))
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        W, H, G, dk, dv = self.hidden_size, self.num_heads, self.num_kv_heads, self.dk, self.dv
+        specs = {"q": TensorSpec((H * dk, W)), "k": TensorSpec((G * dk, W)), "v": TensorSpec((G * dv, W)),
+                 "o": TensorSpec((W, H * dv))}
+        if self.qkv_bias:
+            specs.update({"q.b": TensorSpec((H * dk,), role="vector", init="bias"),
+                          "k.b": TensorSpec((G * dk,), role="vector", init="bias"),
+                          "v.b": TensorSpec((G * dv,), role="vector", init="bias")})
+        if self.head_temps:
+            specs["temp"] = TensorSpec((H,), role="vector", init="norm")
+        if self.sink:
+            specs["sink"] = TensorSpec((H,), role="vector", init="bias")
+        if self.gate:
+            specs["g"] = TensorSpec((H * dv, W))
+        return specs
+
+    def bind(self, tensors):
+        mats = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.gate else [])
+        self.w_in = torch.cat(mats, dim=0).contiguous()        # one product for everything that reads the input
+        if self.qkv_bias:
+            biases = [tensors[n].to(torch.float32) for n in ("q.b", "k.b", "v.b")]
+            if self.gate:
+                biases.append(torch.zeros(tensors["g"].shape[0], dtype=torch.float32, device=biases[0].device))
+            self.b_in = torch.cat(biases).contiguous()
+        self.w_o = tensors["o"]
+        self.temps = tensors["temp"].to(torch.float32).contiguous() if self.head_temps else None
+        self.sinks = tensors["sink"].to(torch.float32).contiguous() if self.sink else None
+
+    def output_weights(self):
+        return [self.w_o]
+
+    def _caches(self, cache: LayerCache):
+        if self.pool is None:
+            Attention._check(cache)
+            return cache, None
+        if cache is None or cache.kind != "several" or len(cache.parts) != 2:
+            raise ValueError("a window attention with block means needs pages for the positions and pages for the blocks")
+        return cache.parts[0], cache.parts[1]
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
+        """The gated heads in front of the output product into ``outs[0]`` [T, heads * vdim]."""
+        kv, blocks = self._caches(cache)
+        if not kv.writes:
+            raise ValueError("this attention keeps its own keys and values")
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dk, self.dv
+        proj = ops.linear(x, self.w_in, self.b_in, out_dtype=torch.float32)
+        pos = self.position
+        freq_v = self.value_position.frequency_pairs() if self.value_position is not None else None
+        q = ops.pooled_prepare(proj, step.positions, pos.frequency_pairs() if pos is not None else None,
+                               pos.rotary_dim if pos is not None else 0, freq_v, step.slots[kv.group], kv.k, kv.v, H, G, dk, dv,
+                               kv.page_size, self.runtime.dtype)
+        if blocks is not None:
+            ops.pooled_means(kv.k, kv.v, blocks.k, blocks.v, step, kv.group, blocks.group, G, dk, dv, kv.page_size, self.pool)
+        gates = proj[:, H * dk + G * (dk + dv):] if self.gate else None
+        ops.pooled_attention(q, outs[0], kv.k, kv.v, blocks.k if blocks is not None else None,
+                             blocks.v if blocks is not None else None, step, kv.group,
+                             blocks.group if blocks is not None else None, H, G, dk, dv, kv.page_size, self.window, self.pool,
+                             self.scale, self.softcap, self.temps, self.sinks, gates, freq_v)
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
+
+register_mixer("pooled_window_attention", PooledWindowAttention)
 register_mixer("latent_attention", LatentAttention)
 register_mixer("attention_maps", MapsAttention)
 register_mixer("attention", Attention)

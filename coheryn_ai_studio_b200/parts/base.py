@@ -45,6 +45,13 @@ class PagedKV:
     window: Optional[int] = None
     v_head_dim: Optional[int] = None      # values of another head size than keys (None: the same; 0: no value rows at
                                           # all, the mixer finds its values inside the key rows)
+    stride: int = 1                       # one row for every ``stride`` positions (a summary of a block of positions): a
+                                          # page then has ceil(page_size / stride) rows, under a block table of its own;
+                                          # the block whose LAST position is p lives in p's page, at row
+                                          # block - floor(page * page_size / stride)
+
+    def rows_per_page(self, page_size: int) -> int:
+        return -(-page_size // self.stride)
 
     @property
     def value_dim(self) -> int:

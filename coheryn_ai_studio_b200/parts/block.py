@@ -17,11 +17,21 @@ from .native_block import NativeBlock
 
 
 class PreNormResidual(Arrangement):
+    """x += mixer(mixer_norm(x)); x += feed_forward(feed_forward_norm(x)); the feed-forward with its norm may be absent."""
+
     SLOTS = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+    OPTIONAL = ("feed_forward", "feed_forward_norm")
+    NAMES = {"mixer_norm": "input_layernorm", "mixer": "self_attn", "feed_forward_norm": "post_attention_layernorm",
+             "feed_forward": "mlp"}
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        if (self.slots.get("feed_forward") is None) != (self.slots.get("feed_forward_norm") is None):
+            raise ValueError("prenorm_residual: a feed-forward comes with its norm or not at all")
 
     def parts(self) -> Dict[str, Part]:
-        return {"input_layernorm": self.mixer_norm, "self_attn": self.mixer,
-                "post_attention_layernorm": self.feed_forward_norm, "mlp": self.feed_forward}
+        names = self.names or self.NAMES
+        return {names[slot]: part for slot, part in self.slots.items() if part is not None}
 
     _native = None     # None: not looked at yet; False: not made of the built-in parts
 
@@ -39,6 +49,8 @@ class PreNormResidual(Arrangement):
                 if out is not None:
                     return residual, out
         mixed = self.mixer.forward(self.mixer_norm.forward(residual, delta), step, cache)
+        if self.feed_forward is None:
+            return residual, mixed
         out = self.feed_forward.forward(self.feed_forward_norm.forward(residual, mixed), step)
         return residual, out
 
@@ -51,6 +63,8 @@ class PreNormResidual(Arrangement):
         if mixed is None:
             return None, None
         kept = ops.gather_rows(residual, step.tail_rows)
+        if self.feed_forward is None:
+            return kept, mixed
         out = self.feed_forward.forward(self.feed_forward_norm.forward(kept, mixed), step.tail)
         return kept, out
 

@@ -149,7 +149,17 @@ class DecoderModel:
         tailed = False
         for i, (entry, cache) in enumerate(zip(self.spec.schedule, caches)):
             layer = self.layers[entry.layer]
-            if entry.inject is not None:
+            if entry.inject is not None and entry.inject.mix is not None:
+                # the stream, with what is pending, beside the embedding output: one kernel makes the product's input,
+                # the product's float32 result is the new stream and nothing is pending
+                if delta is not None and not isinstance(delta, torch.Tensor):
+                    pending = delta.resolve()
+                    delta = None if isinstance(pending, int) else pending
+                joined = ops.stream_join(residual, delta, self.embedding, step.token_ids, self.spec.embedding_scale,
+                                         self.runtime.dtype)
+                residual = ops.linear(joined, self.extra[entry.inject.mix], out_dtype=torch.float32)
+                delta = None
+            elif entry.inject is not None:
                 # added to the stream itself; what the previous entry handed on stays pending beside it
                 vec = entry.inject.vector
                 ops.stream_inject(residual, self.embedding if entry.inject.embedding else None, step.token_ids,

@@ -12,6 +12,13 @@ that runs several mixers side by side.
   u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  Each head's o is divided by its root mean square,
   multiplied by a weight shared by the heads and by sigmoid(W_g2 W_g1 h), then W_o.  The last taps-1 inputs
   of the convolutions are part of the state.
+* ``GatedLinearRecurrence`` (kind ``gated_linear_recurrence``): the recurrent block of Griffin (De et al., "Griffin:
+  Mixing Gated Linear Recurrences with Local Attention for Efficient Language Models") with its real-gated linear
+  recurrent unit.  Two branches of ``width`` channels: y = gelu_tanh(W_y h + b_y) and u = conv(W_x h + b_x), a short
+  causal convolution per channel with a bias and no activation.  u is cut into ``blocks`` equal parts; in part b
+  r = sigmoid(A_b u_b + a_b), i = sigmoid(B_b u_b + c_b) with square matrices.  log a = -``rate`` r softplus(lam);
+  S_t = a S_(t-1) + sqrt(1 - a^2) i u, from S = 0 (no special case for the first token); the output is W_o (S * y).
+  State: S (one float32 per channel) and the convolution's last taps-1 inputs.
 * ``SideBySide`` (kind ``side_by_side``): mixers that read the same input; the result is the weighted sum of
   theirs.  Each child multiplies its own output by its weight before its output projection, and the
   children's outputs go to the next norm as separate summands.
@@ -204,6 +211,66 @@ class GatedDeltaRule(_StateMixer):
                              gate_activation=self.gate_activation)
 
 
+class GatedLinearRecurrence(_StateMixer):
+    def __init__(self, runtime: Runtime, hidden_size: int, width: int, blocks: int, conv_taps: int, rate: float = 8.0,
+                 float32_output: bool = True):
+        super().__init__(runtime)
+        self.hidden_size, self.width, self.blocks, self.taps = int(hidden_size), int(width), int(blocks), int(conv_taps)
+        if self.blocks < 1 or self.width % self.blocks:
+            raise ValueError(f"{self.width} channels do not form {self.blocks} equal blocks")
+        if not 1 <= self.taps <= 16:
+            raise ValueError("the short convolution takes 1 to 16 taps")
+        self.block, self.rate = self.width // self.blocks, float(rate)
+        self.out_dtype = torch.float32 if float32_output else None
+        self.w_in = self.b_in = self.conv_w = self.conv_b = self.w_gates = self.b_r = self.b_i = self.lam = self.w_o = None
+
+    def cache_requirement(self):
+        return FixedState((self.width * self.taps,), torch.float32)      # S, then the convolution's last taps-1 inputs
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        W, C, nb, bs = self.hidden_size, self.width, self.blocks, self.block
+        return {"y": TensorSpec((C, W)), "y.b": TensorSpec((C,), role="vector", init="bias"),
+                "x": TensorSpec((C, W)), "x.b": TensorSpec((C,), role="vector", init="bias"),
+                "conv": TensorSpec((C, self.taps), role="vector", init="conv"),
+                "conv.b": TensorSpec((C,), role="vector", init="bias"),
+                "ra": TensorSpec((nb, bs, bs)), "ra.b": TensorSpec((nb, bs), role="vector", init="bias"),
+                "ri": TensorSpec((nb, bs, bs)), "ri.b": TensorSpec((nb, bs), role="vector", init="bias"),
+                "lam": TensorSpec((C,), role="vector", init="bias"), "o": TensorSpec((W, C))}
+
+    def bind(self, tensors):
+        f32 = lambda t: t.to(torch.float32).contiguous()
+        self.w_in = torch.cat([tensors["y"], tensors["x"]], dim=0).contiguous()       # one product for both branches
+        self.b_in = torch.cat([f32(tensors["y.b"]), f32(tensors["x.b"])]).contiguous()
+        self.conv_w, self.conv_b = f32(tensors["conv"]), f32(tensors["conv.b"])
+        # the gates of a recurrence are float32 arithmetic: per block the rows of both matrices, [r rows | i rows]
+        self.w_gates = torch.cat([f32(tensors["ra"]), f32(tensors["ri"])], dim=1).contiguous()     # [blocks, 2 bs, bs]
+        self.b_r, self.b_i = f32(tensors["ra.b"]).reshape(-1), f32(tensors["ri.b"]).reshape(-1)
+        self.lam, self.w_o = f32(tensors["lam"]), tensors["o"]
+
+    def output_weights(self):
+        return [self.w_o]
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> torch.Tensor:
+        o = torch.empty((x.shape[0], self.width), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
+        o = torch.empty((x.shape[0], self.width), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], outs) -> None:
+        """S * y, the activations in front of the output product, into ``outs[0]`` [T, width]."""
+        state = self._state_of(cache)
+        C, bs = self.width, self.block
+        proj = ops.linear(x, self.w_in, self.b_in, out_dtype=torch.float32)
+        u = ops.conv_bias(proj[:, C:], self.conv_w, self.conv_b, state[:, C:], step)
+        gates = torch.empty((x.shape[0], 2 * C), dtype=torch.float32, device=x.device)
+        ops.grouped_linear(u, self.w_gates, gates, a_col=bs, c_col=2 * bs)
+        ops.gated_scan(gates, self.b_r, self.b_i, u, proj[:, :C], self.lam, self.rate, bs, state[:, :C], step, outs[0])
+
+
 class SideBySide(Mixer):
     def __init__(self, runtime: Runtime, hidden_size: int, mixers: Sequence[Tuple[str, PartSpec, float]], position=None,
                  combine: str = "sum", eps: float = 1e-6):
@@ -290,4 +357,5 @@ class SideBySide(Mixer):
 
 register_mixer("matrix_memory", MatrixMemory)
 register_mixer("gated_delta_rule", GatedDeltaRule)
+register_mixer("gated_linear_recurrence", GatedLinearRecurrence)
 register_mixer("side_by_side", SideBySide)

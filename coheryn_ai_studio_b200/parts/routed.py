@@ -9,6 +9,13 @@ largest choice score, and only outputs of the ``keep`` best groups can be chosen
 the ``top`` largest choice scores are chosen, ties to the lower index.  The weights are the chosen outputs' s divided by
 their sum (+ 1e-20) times ``scale``; the result is the weighted sum of the chosen experts' outputs.
 
+``selection = "top_softmax"`` is the other common router: the choice scores are the logits themselves (plus a bias
+``router.b`` when ``router_bias``), the ``top`` largest are chosen and the weights are the softmax over the chosen logits
+alone (times ``scale``); groups and identity outputs work as above, ``correction`` does not apply.  ``shared``: one more
+expert of the same form (tensors ``shared.gate``, ``shared.up``, ``shared.down``; its own size and activation constant)
+that every token uses; with ``gate`` its output is multiplied by sigmoid(w . x), one number per token (tensor
+``shared.sg`` [1, width]), before it is added.
+
 The pairs (token, choice) that name a real expert are ordered by expert on the device, each expert's rows meet its
 matrices in one grouped product (gate and up interleaved, the activation in the epilogue; then down; with many rows per
 expert the products are the TMA + tcgen05 kernel of the dense layers over row tiles of 128, with fewer the kernel of
@@ -35,8 +42,23 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, runtime: Runtime, hidden_size: int, expert_size: int, experts: int, top: int, identity: int = 0,
                  groups: int = 1, keep: Optional[int] = None, scale: float = 1.0, correction: bool = True,
-                 activation: str = "silu", expert_prefix: str = "e", tensors=("gate", "up", "down")):
+                 activation: str = "silu", expert_prefix: str = "e", tensors=("gate", "up", "down"),
+                 activation_constant: Optional[float] = None, selection: str = "softmax_top", router_bias: bool = False,
+                 shared: Optional[dict] = None):
+        """``shared``: None or {"size": .., "activation_constant": .. (None: the experts'), "gate": bool}."""
         super().__init__(runtime)
+        if selection not in ("softmax_top", "top_softmax"):
+            raise ValueError(f"router selection {selection!r} is not built (softmax_top, top_softmax)")
+        self.selection, self.router_bias = selection, bool(router_bias)
+        if selection == "top_softmax":
+            correction = False
+        elif router_bias:
+            raise ValueError("a bias on the router's logits goes with selection 'top_softmax'")
+        self.shared = None
+        if shared is not None:
+            const = shared.get("activation_constant", activation_constant)
+            self.shared = dict(size=int(shared["size"]), constant=const, gate=bool(shared.get("gate", False)))
+            ops.gated_epilogue_word(activation, const)
         self.hidden_size, self.expert_size = int(hidden_size), int(expert_size)
         self.experts, self.identity, self.top = int(experts), int(identity), int(top)
         self.outputs = self.experts + self.identity
@@ -51,9 +73,9 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"{self.keep} of {self.groups} groups cannot be kept")
         if not 1 <= self.top <= self.keep * (self.outputs // self.groups):
             raise ValueError(f"{self.top} choices do not fit {self.keep} groups of {self.outputs // self.groups}")
-        self.epilogue = ops.gated_epilogue_word(activation, None)
+        self.epilogue = ops.gated_epilogue_word(activation, activation_constant)
         self.activation, self.prefix, self.names = activation, str(expert_prefix), tuple(tensors)
-        self.w_router = self.w_correction = self.w_gate_up = self.w_down = None
+        self.w_router = self.w_correction = self.w_gate_up = self.w_down = self.w_shared_gate_up = self.w_shared_down = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         W, F = self.hidden_size, self.expert_size
@@ -61,6 +83,13 @@ class RoutedExperts(FeedForward):
         specs = {"router": TensorSpec((self.outputs, W))}
         if self.correction:
             specs["correction"] = TensorSpec((self.outputs,), role="vector", init="normal")
+        if self.router_bias:
+            specs["router.b"] = TensorSpec((self.outputs,), role="vector", init="bias")
+        if self.shared is not None:
+            S = self.shared["size"]
+            specs.update({f"shared.{g}": TensorSpec((S, W)), f"shared.{u}": TensorSpec((S, W)), f"shared.{d}": TensorSpec((W, S))})
+            if self.shared["gate"]:
+                specs["shared.sg"] = TensorSpec((1, W))
         for e in range(self.experts):
             p = f"{self.prefix}{e}."
             specs[p + g], specs[p + u], specs[p + d] = TensorSpec((F, W)), TensorSpec((F, W)), TensorSpec((W, F))
@@ -70,6 +99,14 @@ class RoutedExperts(FeedForward):
         g, u, d = self.names
         self.w_router = tensors["router"]
         self.w_correction = tensors["correction"].to(torch.float32).contiguous() if self.correction else None
+        if self.router_bias:
+            self.w_correction = tensors["router.b"].to(torch.float32).contiguous()      # added to the logits: see ``choose``
+        if self.shared is not None:
+            sg_, su_ = tensors[f"shared.{g}"], tensors[f"shared.{u}"]
+            self.w_shared_gate_up = torch.stack([sg_, su_], dim=1).reshape(2 * sg_.shape[0], sg_.shape[1]).contiguous()
+            self.w_shared_down = tensors[f"shared.{d}"]
+            if self.shared["gate"]:      # the gate's row rides under the router's: one product for both
+                self.w_router = torch.cat([self.w_router, tensors["shared.sg"].reshape(1, -1)], dim=0).contiguous()
         # per expert gate and up rows interleaved (2j = gate_j, 2j+1 = up_j): a pair meets in one thread of the epilogue
         gu = [torch.stack([tensors[f"{self.prefix}{e}.{g}"], tensors[f"{self.prefix}{e}.{u}"]], dim=1)
               .reshape(2 * self.expert_size, self.hidden_size) for e in range(self.experts)]
@@ -78,15 +115,25 @@ class RoutedExperts(FeedForward):
 
     def choose(self, x: torch.Tensor):
         """(chosen outputs int32 [T, top], their weights float32 [T, top])."""
+        return self._choose(x)[:2]
+
+    def _choose(self, x: torch.Tensor):
+        """(ids, weights, pre-activation of the shared expert's gate [T] or None)."""
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
-        return ops.route_select(logits, self.w_correction, self.groups, self.keep, self.top, self.scale)
+        ids, weights = ops.route_select(logits[:, :self.outputs], self.w_correction, self.groups, self.keep, self.top, self.scale,
+                                        chosen_softmax=self.selection == "top_softmax")
+        return ids, weights, logits[:, self.outputs] if logits.shape[1] > self.outputs else None
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         T = x.shape[0]
         out = torch.empty((T, self.hidden_size), dtype=torch.float32, device=x.device)
         if T == 0:
             return out
-        ids, weights = self.choose(x)
+        ids, weights, shared_gate = self._choose(x)
+        shared = None
+        if self.shared is not None:
+            act = ops.gated_linear(x, self.w_shared_gate_up, self.activation, param=self.shared["constant"])
+            shared = ops.linear(act, self.w_shared_down, out_dtype=torch.float32)
         wide = ops.grouped_tc_suits(x, T * self.top, self.experts, self.w_gate_up, self.w_down)
         rows = ops.route_sort(ids, self.experts, wide_tiles=wide)
         n = rows.n
@@ -98,7 +145,7 @@ class RoutedExperts(FeedForward):
         else:
             ops.grouped_linear(x, self.w_gate_up, act, rows=rows, gather=True, epilogue=self.epilogue)
             ops.grouped_linear(act, self.w_down, y, rows=rows)
-        ops.route_combine(y, x, ids, weights, rows, out)
+        ops.route_combine(y, x, ids, weights, rows, out, extra=shared, extra_gate=shared_gate)
         return out
 
 
