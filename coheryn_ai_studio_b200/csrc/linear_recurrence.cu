@@ -8,11 +8,15 @@
 //                  S_t = a S_(t-1) + sqrt(1 - a^2) * i * u, out_t = S_t * gelu_tanh(y_t) (y: the other branch's pre-activation).
 //
 // Everything is float32.  The scan is parallel over channels AND over chunks of consecutive tokens of the step: a first
-// kernel scans every chunk from zero and leaves (product of a, end value) per chunk and channel; the second one walks
+// kernel scans every chunk from zero and leaves (sum of log a, end value) per chunk and channel; the second one walks
 // over the summaries of the chunks between its request's start and itself (at most tokens / chunk steps), then scans
 // its chunk again from the true start value and writes the outputs.  A request's first token of the step starts from
 // the request's state; the token that ends a request's run stores the state.  The order of a channel's additions is
 // fixed by the token's place in its request's run, not by the other requests of the step.
+//
+// a is never formed: a value near 1 would be rounded to a neighbour of 1 that decays several per cent faster or slower
+// (or not at all), always to the same side, and over a thousand tokens that bias shows.  With a - 1 = expm1(log a) the step
+// is S <- (S + (a - 1) S) + d, whose roundings are those of S and scatter.
 #include "common.cuh"
 
 namespace {
@@ -81,14 +85,15 @@ struct ScanArgs {
 __device__ __forceinline__ float lr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float lr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// (a, drive) of token t and channel c; sp = rate * softplus(lam[c]).
-__device__ __forceinline__ void lr_coefficients(const ScanArgs& A, int t, int c, float sp, float b_r, float b_i, float& a, float& d) {
+// (log a, a - 1, drive) of token t and channel c; sp = rate * softplus(lam[c]).
+__device__ __forceinline__ void lr_coefficients(const ScanArgs& A, int t, int c, float sp, float b_r, float b_i, float& log_a,
+                                                float& am1, float& d) {
   const int blk = c / A.bs, j = c - blk * A.bs;
   const float* g = A.gates + (size_t)t * A.ldg + (size_t)blk * 2 * A.bs;
   const float r = lr_sigmoid(g[j] + b_r);
   const float i = lr_sigmoid(g[A.bs + j] + b_i);
-  const float log_a = -sp * r;
-  a = expf(log_a);
+  log_a = -sp * r;
+  am1 = expm1f(log_a);
   d = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f)) * i * A.u[(size_t)t * A.ldu + c];
 }
 
@@ -101,20 +106,20 @@ __global__ void __launch_bounds__(LANES) scan_summaries_kernel(ScanArgs A) {
   const float b_r = A.br ? co_load_any(A.br, A.b_dtype, c) : 0.f, b_i = A.bi ? co_load_any(A.bi, A.b_dtype, c) : 0.f;
   co_pdl_wait();
   const int t0 = chunk * CHUNK, t1 = min(t0 + CHUNK, A.T);
-  float prod = 1.f, S = 0.f;
+  float logs = 0.f, S = 0.f;
   for (int t = t0; t < t1; ++t) {
     const int r = A.token_req[t];
     if (t == A.cu_q[r]) {        // a request's run begins: what came before does not reach beyond this token
       S = A.state[(size_t)A.state_slots[r] * A.state_stride + c];
       A.first[(size_t)r * A.C + c] = S;
-      prod = 0.f;
+      logs = -INFINITY;
     }
-    float a, d;
-    lr_coefficients(A, t, c, sp, b_r, b_i, a, d);
-    S = fmaf(a, S, d);
-    prod *= a;
+    float log_a, am1, d;
+    lr_coefficients(A, t, c, sp, b_r, b_i, log_a, am1, d);
+    S = fmaf(am1, S, S) + d;
+    logs += log_a;
   }
-  A.carry_a[(size_t)chunk * A.C + c] = prod;
+  A.carry_a[(size_t)chunk * A.C + c] = logs;
   A.carry_s[(size_t)chunk * A.C + c] = S;
 }
 
@@ -136,16 +141,17 @@ __global__ void __launch_bounds__(LANES) scan_outputs_kernel(ScanArgs A) {
     if (start < t0) {
       const int c0 = start / CHUNK;     // its end value belongs to this request: the request runs on into this chunk
       S = A.carry_s[(size_t)c0 * A.C + c];
-      for (int k = c0 + 1; k < chunk; ++k) S = fmaf(A.carry_a[(size_t)k * A.C + c], S, A.carry_s[(size_t)k * A.C + c]);
+      for (int k = c0 + 1; k < chunk; ++k)
+        S = fmaf(expm1f(A.carry_a[(size_t)k * A.C + c]), S, S) + A.carry_s[(size_t)k * A.C + c];
     }
   }
   TO* out = (TO*)A.out;
   for (int t = t0; t < t1; ++t) {
     const int r = A.token_req[t];
     if (t == A.cu_q[r]) S = A.first[(size_t)r * A.C + c];
-    float a, d;
-    lr_coefficients(A, t, c, sp, b_r, b_i, a, d);
-    S = fmaf(a, S, d);
+    float log_a, am1, d;
+    lr_coefficients(A, t, c, sp, b_r, b_i, log_a, am1, d);
+    S = fmaf(am1, S, S) + d;
     out[(size_t)t * A.ldo + c] = co_from_float<TO>(S * co_gelu_tanh(A.y[(size_t)t * A.ldy + c]));
     if (t + 1 == A.cu_q[r + 1]) A.state[(size_t)A.state_slots[r] * A.state_stride + c] = S;
   }
