@@ -27,7 +27,9 @@ which no graph replays: it measures what such steps cost the host.  ``--workload
 (matrix-memory layers and attention beside a gated delta rule) at two layer sizes beside Qwen2 at equal sizes: prefill and
 decode through the step function, and the mixers' kernels alone.  ``--workload tutunex`` does the same for the Tutunex
 design (differential attention over chunks, attention with a sink beside a gated delta rule, norms before and after each
-sub-layer), its kernels beside the like kernels of the other models.  ``--workload guvusun`` does the same for the Guvusun
+sub-layer), its kernels beside the like kernels of the other models.  ``--workload zegelix`` does the same for the Zegelix
+design (gated linear recurrences, window attention over positions and block means, routed experts with a shared expert, a
+repeated span of layers).  ``--workload guvusun`` does the same for the Guvusun
 design (latent attention with a learned sink and head gates, routed experts, norms after the sum) beside Qwen2 with a dense
 feed-forward of the experts' active size.
 """
@@ -811,6 +813,153 @@ def guvusun_workload(args) -> int:
     return 0
 
 
+# Sizes of --workload zegelix.  Layers in the proportion two recurrences : one window attention, a span of the stack run
+# twice, routed experts with a shared expert in every layer.  Qwen2 beside each at equal width, as many layers as the design
+# has layer RUNS, the same heads and head size, and a dense feed-forward of (top + shared) x expert size (the same active
+# matrix rows per token).
+ZEGELIX_SIZES = {
+    "w2048": dict(width=2048, rwidth=2560, blocks=16, conv=4, heads=16, kv_heads=4, dim=128, window=1024, pool=32, experts=32, top=4,
+                  ff=1024, shared=1024, vocab=32000, kinds="rra" "rra", loop=(0, 3, 2)),
+    "w4096": dict(width=4096, rwidth=4096, blocks=16, conv=4, heads=32, kv_heads=8, dim=128, window=2048, pool=64, experts=64, top=6,
+                  ff=1408, shared=2816, vocab=32000, kinds="rar", loop=(0, 3, 2)),
+}
+
+
+def zegelix_config(z):
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared"], "limit": 7.0}}
+    rec = {"type": "rglru", "mixer": {"width": z["rwidth"], "blocks": z["blocks"], "conv": z["conv"]}, "mlp": mlp}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                     "softcap": 50.0, "rot": {"dims": z["dim"], "base": 10000.0}, "mask": {"size": z["window"], "pool": z["pool"]}}}
+    return {"architecture": "Zegelix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "loop": {"start": z["loop"][0], "stop": z["loop"][1], "times": z["loop"][2]},
+            "layers": [rec if c == "r" else att for c in z["kinds"]]}
+
+
+def zegelix_workload(args) -> int:
+    """Prefill and decode throughput of Zegelix and of Qwen2 at equal sizes through the step function, and the design's own
+    kernels alone beside the like kernels of the other models, each with its share of the roofline.  One JSON line."""
+    import numpy as np
+    import torch
+
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.config.zegelix import ZegelixConfig
+    from coheryn_ai_studio_b200.engine import random_model_on_device
+
+    tools = model_bench_tools(args)
+    pk, hbm, flops_peak, dev = tools.pk, tools.hbm, tools.flops_peak, tools.dev
+    tokens, batch, context = tools.tokens, tools.batch, tools.context
+    timed, step_like = tools.timed, tools.step_like
+    fma_peak = 148 * 128 * 2 * 1.965e9        # float32 FMA lanes x 2 x the SM clock: what float32 arithmetic is bound by
+
+    def kernels(z):
+        out = {}
+        H, G, d, W, C, page = z["heads"], z["kv_heads"], z["dim"], z["width"], z["rwidth"], args.page_size
+        size, pool, bs, taps = z["window"], z["pool"], z["rwidth"] // z["blocks"], z["conv"]
+        f = lambda *shape: torch.randn(shape, device=dev)
+        b16 = lambda *shape: f(*shape).to(torch.bfloat16)
+        for name, lengths, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            B, T = len(lengths), sum(lengths)
+            per = -(-max(s + n for s, n in zip(starts, lengths)) // page)
+            tables = torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per)
+            st = step_like(lengths, starts, tables)
+            st.block_tables = [tables, tables]
+            st.slots = [(tables[st.token_req.long(), (st.positions // page).long()] * page + st.positions % page).to(torch.int32)]
+            rows = -(-page // pool)
+            kc, vc = b16(B * per + 1, G, page, d), b16(B * per + 1, G, page, d)
+            pkc, pvc = b16(B * per + 1, G, rows, d), b16(B * per + 1, G, rows, d)
+            # keys a row meets: its window and the blocks behind it
+            met = sum(min(p + 1, size) + max(0, (p - size + 1) // pool) for s, n in zip(starts, lengths) for p in range(s, s + n))
+            met_window = sum(min(p + 1, size) for s, n in zip(starts, lengths) for p in range(s, s + n))
+            held = sum(min(s + n, size + n) + (s + n) // pool for s, n in zip(starts, lengths))      # cached rows that are read
+
+            def attention(label, fn, keys, rows_read):
+                ms = timed(fn)
+                fl = 2.0 * H * 2 * d * keys
+                by = 4.0 * d * G * rows_read + 4.0 * T * H * d
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1),
+                                          "of_bf16_peak": round(fl / (ms / 1e3) / flops_peak, 4), "of_hbm": round(by / (ms / 1e3) / hbm, 4)}
+            q, o = b16(T, H * d), torch.empty((T, H * d), dtype=torch.bfloat16, device=dev)
+            temps, sinks, gates = f(H).abs() + 0.5, f(H), f(T, H * d)
+            fv = torch.stack([torch.pow(torch.tensor(10000.0), -2.0 * torch.arange(d // 2) / d), torch.zeros(d // 2)], dim=1).to(dev).contiguous()
+            attention("window_and_blocks_attention", lambda: ops.pooled_attention(
+                q, o, kc, vc, pkc, pvc, st, 0, 1, H, G, d, d, page, size, pool, d ** -0.5, 50.0, temps, sinks, gates, fv), met, held)
+            attention("qwen2_attention_same_window", lambda: ops.attention_rows(
+                q, o, kc, vc, tables, st.token_req, st.positions, H, G, d, page, size, d ** -0.5, cu_q=st.cu_q, kv_lens=st.kv_lens,
+                q_lens=st.q_lens, max_kv_len=st.max_kv_len), met_window, sum(min(s + n, size + n) for s, n in zip(starts, lengths)))
+
+            def by_bytes(label, fn, by, flops=None, peak=None):
+                ms = timed(fn)
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "of_hbm": round(by / (ms / 1e3) / hbm, 4)}
+                if flops is not None:
+                    out[f"{name}.{label}"]["of_flop_peak"] = round(flops / (ms / 1e3) / peak, 4)
+            proj = f(T, (H + 2 * G) * d + H * d)
+            fk = fv
+            by_bytes("rotate_q_k_v_and_write_cache", lambda: ops.pooled_prepare(
+                proj, st.positions, fk, d, fv, st.slots[0], kc, vc, H, G, d, d, page, torch.bfloat16), T * (H + 2 * G) * d * 6.0)
+            from coheryn_ai_studio_b200.parts.base import Runtime
+            from coheryn_ai_studio_b200.parts.position import RotateHalfRope
+            rope = RotateHalfRope(Runtime(torch.bfloat16, dev), head_dim=d, rotary_dim=d, theta=10000.0, max_positions=context + tokens + 64)
+            qkv = b16(T, (H + 2 * G) * d)
+            by_bytes("qwen2_rotate_and_write_cache", lambda: ops.rope_kv_write(
+                qkv, st.positions, rope.cos_sin(), st.slots[0], kc, vc, H, G, d, d, page), T * (H + 2 * G) * d * 4.0)
+            by_bytes("block_means", lambda: ops.pooled_means(kc, vc, pkc, pvc, st, 0, 1, G, d, d, page, pool),
+                     (T // pool + B) * pool * 2 * G * d * 2.0)
+            # the recurrence: convolution, the gates' block-diagonal products (float32 FMA), the scan
+            state = torch.zeros((B, C * taps), dtype=torch.float32, device=dev)
+            x, u, y = f(T, C), f(T, C), f(T, C)
+            conv_w, conv_b = f(C, taps), f(C)
+            by_bytes("conv_with_bias", lambda: ops.conv_bias(x, conv_w, conv_b, state[:, C:], st), T * C * 8.0)
+            from coheryn_ai_studio_b200 import ops as _ops
+            by_bytes("tutunex_conv_silu", lambda: _ops.short_conv_silu(x, conv_w, state[:, C:], st), T * C * 8.0)
+            wg, gts = f(z["blocks"], 2 * bs, bs), torch.empty((T, 2 * C), dtype=torch.float32, device=dev)
+            by_bytes("gates_float32_fma", lambda: ops.grouped_linear(u, wg, gts, a_col=bs, c_col=2 * bs),
+                     T * C * 12.0 + wg.numel() * 4.0, flops=2.0 * T * 2 * C * bs, peak=fma_peak)
+            lam, br, bi = f(C) - 4.0, f(C), f(C)
+            so = torch.empty((T, C), dtype=torch.bfloat16, device=dev)
+            by_bytes("gated_scan", lambda: ops.gated_scan(gts, br, bi, u, y, lam, 8.0, bs, state[:, :C], st, so),
+                     T * C * (2 * 12.0 + 4.0 + 2.0))
+            xs, table = f(T, W), b16(z["vocab"], W)
+            st.token_ids = torch.randint(0, z["vocab"], (T,), dtype=torch.int32, device=dev)
+            by_bytes("stream_beside_embedding", lambda: ops.stream_join(xs, None, table, st.token_ids, 1.0, torch.bfloat16), T * W * 10.0)
+        return out
+
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    results = {}
+    chosen = [n for n in ZEGELIX_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in chosen:
+        z = ZEGELIX_SIZES[name]
+        entry = {}
+        cfg = ZegelixConfig.from_dict(zegelix_config(z))
+        model = random_model_on_device(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+        runs = len(model.spec.schedule)
+        entry["zegelix"] = tools.run_model(model, z["vocab"])
+        del model
+        torch.cuda.empty_cache()
+        qcfg = Qwen2Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["top"] * z["ff"] + z["shared"],
+                           num_hidden_layers=runs, num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                           head_dim=z["dim"], max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6,
+                           tie_word_embeddings=False)
+        model = random_model_on_device(qcfg, seed=0, dtype="bfloat16", device="cuda:0")
+        entry["qwen2_equal_size"] = tools.run_model(model, z["vocab"])
+        entry["layer_runs"] = runs
+        del model
+        torch.cuda.empty_cache()
+        if not args.no_kernels:
+            entry["kernels"] = kernels(z)
+        results[name] = entry
+    clocks = ClockSampler.summary(sampler.window(t0, time.time()))
+    sampler.stop()
+    print(json.dumps({"workload": "zegelix", "dtype": "bf16", "data": "synthetic", "prefill_tokens": tokens, "decode_batch": batch,
+                      "decode_context": context, "decode_steps": tools.steps, "peaks": pk, "clocks": clocks,
+                      "l2": "flushed before each timed kernel", "gpu_launches": ops.total_launch_count(), "sizes": results}))
+    return 0
+
+
 def timeline(args, make_engine, StepEntry, ops, torch) -> int:
     """Where a decode step's time goes, kernel by kernel, measured inside graph-replayed steps (the
     kernels overlap through programmatic dependent launch, so a kernel's own duration says little):
@@ -878,10 +1027,10 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b", "kapudra", "tutunex", "guvusun"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b", "kapudra", "tutunex", "guvusun", "zegelix"],
                     help="decode: the contract's line (default); the others: see the header")
-    ap.add_argument("--sizes", default="", help="--workload kapudra / tutunex / guvusun: which of its sizes (comma separated; default all)")
-    ap.add_argument("--no-kernels", action="store_true", help="--workload guvusun: the models only, not the kernels alone")
+    ap.add_argument("--sizes", default="", help="--workload kapudra / tutunex / guvusun / zegelix: which of its sizes (comma separated; default all)")
+    ap.add_argument("--no-kernels", action="store_true", help="--workload guvusun / zegelix: the models only, not the kernels alone")
     ap.add_argument("--timeline-raw", action="store_true", help="with --timeline: also every kernel's start and end")
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the benchmark: the kernels of one graph-replayed decode step with their times "
@@ -904,6 +1053,8 @@ def main() -> int:
         return tutunex_workload(args)
     if args.workload == "guvusun":
         return guvusun_workload(args)
+    if args.workload == "zegelix":
+        return zegelix_workload(args)
     if args.workload != "decode":
         return other_workload(args)
 

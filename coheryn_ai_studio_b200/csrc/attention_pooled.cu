@@ -16,9 +16,9 @@
 //                     cache in position order, into the block cache: a second set of pages under a block table of its
 //                     own with ceil(page_size / pool) rows per page; block b lives in the page of its LAST position p,
 //                     at row b - floor(page(p) * page_size / pool);
-//   * pooled_attention: one CTA per (row, head): four warps take the keys in turn (a key's place among the row's keys
-//                     decides its warp, so a row's sums do not depend on the batch), online softmax per warp, merged in
-//                     warp order.
+//   * pooled_attention: one CTA per (row, head): eight warps take the keys in turn, four neighbouring keys at a time (a
+//                     key's place among the row's keys decides its warp, so a row's sums do not depend on the batch),
+//                     online softmax per warp, merged in warp order.
 #include "common.cuh"
 
 namespace {
@@ -127,7 +127,8 @@ struct AttnArgs {
   float scale, cap;
 };
 
-constexpr int PA_WARPS = 4;
+constexpr int PA_WARPS = 8;
+constexpr int PA_KEYS = 4;          // keys a warp takes at a time
 constexpr int PA_MAX_PER_LANE = 8;     // channels per lane: head sizes up to 256
 
 template <typename TT>
@@ -161,39 +162,66 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_kernel(AttnArg
     acc[e] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
-  for (int n = warp; n < total; n += PA_WARPS) {
-    const TT* kr;
-    const TT* vr;
-    if (n < nb) {
-      const long last = (long)n * A.pool + A.pool - 1;
-      const int lp = (int)(last / A.page_size);
-      const int row = n - (int)(((long)lp * A.page_size) / A.pool);
-      const size_t page = (size_t)A.pool_tables[(size_t)r * A.pool_table_width + lp];
-      const size_t at = (page * A.G + g) * A.pool_rows + row;
-      kr = (const TT*)A.pk + at * dk;
-      vr = (const TT*)A.pv + at * dv;
-    } else {
-      const int pos = lo + (n - nb);
-      const size_t page = (size_t)table[pos / A.page_size];
-      const size_t at = (page * A.G + g) * A.page_size + (size_t)(pos % A.page_size);
-      kr = (const TT*)A.k + at * dk;
-      vr = (const TT*)A.v + at * dv;
-    }
-    float s = 0.f;
+  // a warp takes PA_KEYS neighbouring keys at a time (their rows are requested together), the warps in turn
+  for (int n0 = warp * PA_KEYS; n0 < total; n0 += PA_WARPS * PA_KEYS) {
+    const TT* kr[PA_KEYS];
+    const TT* vr[PA_KEYS];
 #pragma unroll
-    for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
-      const int c = lane + 32 * e;
-      if (c < dk) s = fmaf(qreg[e], co_to_float<TT>(kr[c]), s);
+    for (int b = 0; b < PA_KEYS; ++b) {
+      const int n = min(n0 + b, total - 1);
+      if (n < nb) {
+        const long last = (long)n * A.pool + A.pool - 1;
+        const int lp = (int)(last / A.page_size);
+        const int row = n - (int)(((long)lp * A.page_size) / A.pool);
+        const size_t page = (size_t)A.pool_tables[(size_t)r * A.pool_table_width + lp];
+        const size_t at = (page * A.G + g) * A.pool_rows + row;
+        kr[b] = (const TT*)A.pk + at * dk;
+        vr[b] = (const TT*)A.pv + at * dv;
+      } else {
+        const int pos = lo + (n - nb);
+        const size_t page = (size_t)table[pos / A.page_size];
+        const size_t at = (page * A.G + g) * A.page_size + (size_t)(pos % A.page_size);
+        kr[b] = (const TT*)A.k + at * dk;
+        vr[b] = (const TT*)A.v + at * dv;
+      }
     }
-    s = co_warp_sum(s) * mult;
-    if (A.cap > 0.f) s = A.cap * tanhf(s / A.cap);
-    const float m_new = fmaxf(m, s);
-    const float f = expf(m - m_new), w = expf(s - m_new);      // exp(-inf) = 0 for the first key
-    l = l * f + w;
+    float s[PA_KEYS];
 #pragma unroll
-    for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
-      const int c = lane + 32 * e;
-      if (c < dv) acc[e] = fmaf(w, co_to_float<TT>(vr[c]), acc[e] * f);
+    for (int b = 0; b < PA_KEYS; ++b) {
+      s[b] = 0.f;
+#pragma unroll
+      for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
+        const int c = lane + 32 * e;
+        if (c < dk) s[b] = fmaf(qreg[e], co_to_float<TT>(kr[b][c]), s[b]);
+      }
+    }
+    float vals[PA_KEYS][PA_MAX_PER_LANE];
+#pragma unroll
+    for (int b = 0; b < PA_KEYS; ++b) {
+#pragma unroll
+      for (int e = 0; e < PA_MAX_PER_LANE; ++e) {
+        const int c = lane + 32 * e;
+        vals[b][e] = c < dv ? co_to_float<TT>(vr[b][c]) : 0.f;
+      }
+    }
+    float m_new = m;
+#pragma unroll
+    for (int b = 0; b < PA_KEYS; ++b) {
+      float x = co_warp_sum(s[b]) * mult;
+      if (A.cap > 0.f) x = A.cap * tanhf(x / A.cap);
+      s[b] = n0 + b < total ? x : -INFINITY;
+      m_new = fmaxf(m_new, s[b]);
+    }
+    const float f = expf(m - m_new);       // exp(-inf) = 0 before the warp's first key
+    l *= f;
+#pragma unroll
+    for (int e = 0; e < PA_MAX_PER_LANE; ++e) acc[e] *= f;
+#pragma unroll
+    for (int b = 0; b < PA_KEYS; ++b) {
+      const float w = expf(s[b] - m_new);
+      l += w;
+#pragma unroll
+      for (int e = 0; e < PA_MAX_PER_LANE; ++e) acc[e] = fmaf(w, vals[b][e], acc[e]);
     }
     m = m_new;
   }

@@ -263,6 +263,15 @@ def pooled_attention_library() -> ctypes.CDLL:
     return load_library("pooled_attention", POOLED_ATTENTION_SOURCES)
 
 
+def pooled_attention_tc_library(dk: int, dv: int) -> ctypes.CDLL:
+    """The tensor-core kernel of the window attention over positions and block means, compiled for one (key channels,
+    value channels) when a model needs it."""
+    if dk % 16 or dv % 16 or not 16 <= dk <= 256 or not 16 <= dv <= 128:
+        raise BuildError(f"the tensor-core window attention takes key channels 16..256 and value channels 16..128 in steps "
+                         f"of 16, not ({dk}, {dv})")
+    return load_library(f"pooled_tc_{dk}_{dv}", ["attention_pooled_tc.cu", "runtime.cu"], {"CO_PW_DK": dk, "CO_PW_DV": dv})
+
+
 def routed_library() -> ctypes.CDLL:
     """Routing of tokens to experts and matrix products over groups of rows that each meet a matrix of their own (experts,
     or the heads of an attention with a matrix per head).  Compiled when a model with such a part is first run."""
@@ -290,7 +299,8 @@ def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     paths = [build_host_library(), build_library("core", CORE_SOURCES), build_library("recurrent", RECURRENT_SOURCES),
              build_library("variants", VARIANT_SOURCES), build_library("routed", ROUTED_SOURCES),
              build_library("linear_recurrence", LINEAR_RECURRENCE_SOURCES),
-             build_library("pooled_attention", POOLED_ATTENTION_SOURCES)]
+             build_library("pooled_attention", POOLED_ATTENTION_SOURCES),
+             build_library("pooled_tc_128_128", ["attention_pooled_tc.cu", "runtime.cu"], {"CO_PW_DK": 128, "CO_PW_DV": 128})]
     paths.append(build_library("maps_96_64_1_vk", ["attention_maps_tc.cu", "runtime.cu"],
                                {"CO_MAPS_DK": 96, "CO_MAPS_DV": 64, "CO_MAPS_N": 1, "CO_MAPS_V_IN_K": 1}))
     for dk, dv, maps in ((64, 128, 2), (64, 64, 1)):

@@ -1640,6 +1640,33 @@ def pooled():
     return _pooled
 
 
+_pooled_tc_libs = {}
+# Whether bfloat16 prompt portions take the tensor-core kernel of the window attention (the float32-arithmetic kernel
+# otherwise); for tests and measurements.
+POOLED_TC = os.environ.get("COHERYN_POOLED_TC", "1") != "0"
+# From how many rows of its longest request a step takes the tensor-core kernel (its row tiles hold 64).
+POOLED_TC_MIN_ROWS = int(os.environ.get("COHERYN_POOLED_TC_MIN_ROWS", "5"))
+
+
+def set_pooled_tc(on: bool) -> None:
+    global POOLED_TC
+    POOLED_TC = bool(on)
+
+
+def pooled_tc_lib(dk: int, dv: int):
+    lib = _pooled_tc_libs.get((dk, dv))
+    if lib is None:
+        lib = build.pooled_attention_tc_library(dk, dv)
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        got = [ctypes.c_int(), ctypes.c_int()]
+        lib.coheryn_pooled_tc_shape(*[ctypes.byref(g) for g in got])
+        if tuple(g.value for g in got) != (dk, dv):
+            raise KernelError(f"the window attention library was built for {tuple(g.value for g in got)}, not {(dk, dv)}")
+        _pooled_tc_libs[(dk, dv)] = lib
+    return lib
+
+
 def pooled_prepare(proj: torch.Tensor, positions: torch.Tensor, freq_k: Optional[torch.Tensor], rot: int,
                    freq_v: Optional[torch.Tensor], slots: Optional[torch.Tensor], k_cache, v_cache, heads: int, kv_heads: int,
                    dk: int, dv: int, page_size: int, dtype: torch.dtype) -> torch.Tensor:
@@ -1708,6 +1735,21 @@ def pooled_attention(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, pk_ca
         assert gates.shape == (T, heads * dv)
     if pool and not window:
         raise KernelError("pooled_attention: block means stand for positions before a window; without a window there are none")
+    q_lens = getattr(step, "q_lens", None)
+    if (POOLED_TC and q.dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and dk <= 256 and dv <= 128 and q_lens
+            and max(q_lens) >= POOLED_TC_MIN_ROWS and getattr(step, "cu_q", None) is not None and q.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        # rows that are whole runs of consecutive positions per request, ending at the request's last position
+        _dev(step.cu_q, step.kv_lens)
+        lib = pooled_tc_lib(dk, dv)
+        _check(lib, lib.coheryn_pooled_attention_tc(
+            _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(pk_cache),
+            _ptr(pv_cache), _ptr(tables), c_int(tables.shape[1]), _ptr(ptables), c_int(ptables.shape[1] if ptables is not None else 0),
+            _ptr(step.cu_q), _ptr(step.kv_lens), _ptr(temps), _ptr(sinks), _ptr(gates),
+            c_long(gates.stride(0) if gates is not None else 0), _ptr(freq_v), c_int(len(q_lens)), c_int(max(q_lens)), c_int(heads),
+            c_int(kv_heads), c_int(page_size), c_int(window or 0), c_int(pool or 0), c_int(pk_cache.shape[2] if pool else 0),
+            c_float(scale), c_float(softcap or 0.0), _stream()))
+        return
     lib = pooled()
     _check(lib, lib.coheryn_pooled_attention(
         _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(pk_cache),

@@ -107,36 +107,49 @@ def visible_blocks(i, size, pool):
     return max(0, (i - size + 1) // pool)
 
 
+def attend_window_and_blocks(q, k, v, size, pool, scale, cap, temp=None, sink=None, rounder=_same):
+    """q [T, H, dk], k [T, G, dk], v [T, G, dv] as the cache holds them (positions 0..T-1).  Row i attends over the
+    positions j with 0 <= i - j < size and over the means of the blocks of ``pool`` positions that lie wholly before them
+    (``pool`` None: none); score = q . k * scale * temp[h], capped by cap * tanh(. / cap) (``cap`` None: not); the
+    denominator has the extra term exp(sink[h]) (``sink`` None: not).  Returns [T, H, dv]."""
+    T, H, dk = q.shape
+    G, dv = k.shape[1], v.shape[2]
+    if pool is not None:
+        nb = T // pool
+        pk = rounder(k[:nb * pool].reshape(nb, pool, G, dk).mean(1))
+        pv = rounder(v[:nb * pool].reshape(nb, pool, G, dv).mean(1))
+    out = np.zeros((T, H, dv))
+    for i in range(T):
+        n = visible_blocks(i, size, pool) if pool is not None else 0
+        lo = max(0, i - size + 1) if size is not None else 0
+        for hh in range(H):
+            g = hh // (H // G)
+            keys, vals = k[lo:i + 1, g], v[lo:i + 1, g]
+            if n:
+                keys, vals = np.concatenate([pk[:n, g], keys], axis=0), np.concatenate([pv[:n, g], vals], axis=0)
+            s = (keys @ q[i, hh]) * scale * (temp[hh] if temp is not None else 1.0)
+            if cap is not None:
+                s = cap * np.tanh(s / cap)
+            top = s.max() if sink is None else max(s.max(), sink[hh])
+            e = np.exp(s - top)
+            out[i, hh] = (e @ vals) / (e.sum() + (math.exp(sink[hh] - top) if sink is not None else 0.0))
+    return out
+
+
 def pooled_window_attention(h, positions, W, p, m, rounder=_same):
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    size, pool = m["mask"]["size"], m["mask"]["pool"]
-    rot, cap = m["rot"], m["softcap"]
+    rot = m["rot"]
+    assert list(positions) == list(range(T)), "the plain attention keeps no cache: positions count from 0"
     q = (h @ W[p + "q"].T + W[p + "q.b"]).reshape(T, H, dk)
     k = (h @ W[p + "k"].T + W[p + "k.b"]).reshape(T, G, dk)
     v = (h @ W[p + "v"].T + W[p + "v.b"]).reshape(T, G, dv)
     q = rounder(rotate_halves(q, positions, rot["dims"], rot["base"]))
     k = rounder(rotate_halves(k, positions, rot["dims"], rot["base"]))
-    v = rounder(rotate_halves(v, positions, dv, rot["base"]))
-    assert list(positions) == list(range(T)), "the plain attention keeps no cache: positions count from 0"
-    nb = T // pool
-    pk = rounder(k[:nb * pool].reshape(nb, pool, G, dk).mean(1))
-    pv = rounder(v[:nb * pool].reshape(nb, pool, G, dv).mean(1))
-    temp, sink = W[p + "temp"], W[p + "sink"]
-    out = np.zeros((T, H, dv))
-    for i in range(T):
-        n = visible_blocks(i, size, pool)
-        lo = max(0, i - size + 1)
-        for hh in range(H):
-            g = hh // (H // G)
-            keys = np.concatenate([pk[:n, g], k[lo:i + 1, g]], axis=0)
-            vals = np.concatenate([pv[:n, g], v[lo:i + 1, g]], axis=0)
-            s = (keys @ q[i, hh]) * m["scale"] * temp[hh]
-            s = cap * np.tanh(s / cap)
-            top = max(s.max(), sink[hh])
-            e = np.exp(s - top)
-            out[i, hh] = (e @ vals) / (e.sum() + math.exp(sink[hh] - top))
-    out = rotate_halves(out, positions, dv, rot["base"], sign=-1.0)
+    v = rounder(rotate_halves(v, positions, dv, rot["base"]))       # a value is cached turned by its own position ...
+    out = attend_window_and_blocks(q, k, v, m["mask"]["size"], m["mask"]["pool"], m["scale"], m["softcap"], W[p + "temp"],
+                                   W[p + "sink"], rounder)
+    out = rotate_halves(out, positions, dv, rot["base"], sign=-1.0)  # ... and the sum is turned back by the query's
     gate = sigmoid(h @ W[p + "g"].T)
     return rounder(out.reshape(T, H * dv) * gate) @ W[p + "o"].T
 
