@@ -34,50 +34,66 @@ __device__ __forceinline__ void pa_sincos(float p, const float* freq, int i, flo
   s = sh * cl + ch * sl;
 }
 
-// grid (T, heads + 2 * kv_heads); proj float32 [T, ld]: queries from column 0, keys from q_cols, values behind them.
+// grid (T); proj float32 [T, ld]: queries from column 0, keys from q_cols, values behind them.  The cosines and sines of
+// the row's position are made once (shared memory) and serve all heads.
 template <typename TT>
 __global__ void pooled_prepare_kernel(const float* __restrict__ proj, long ld, const int* __restrict__ positions,
                                       const float* __restrict__ freq_k, int rot, const float* __restrict__ freq_v,
                                       TT* __restrict__ q_out, long ldq, const int* __restrict__ slots, TT* __restrict__ k_cache,
                                       TT* __restrict__ v_cache, int H, int G, int dk, int dv, int page_size) {
+  extern __shared__ __align__(16) float sm[];
   co_pdl_launch_dependents();
-  co_pdl_wait();
   const size_t t = blockIdx.x;
-  const int unit = blockIdx.y;
+  const int hk = rot / 2, hv = freq_v ? dv / 2 : 0;
+  float* cs_k = sm;               // [hk][2]
+  float* cs_v = sm + 2 * hk;      // [hv][2]
+  co_pdl_wait();
   const float p = (float)positions[t];
-  const float* src;
-  TT* dst;
-  int n, turned;
-  const float* freq;
-  if (unit < H) {
-    src = proj + t * ld + (size_t)unit * dk;
-    dst = q_out + t * ldq + (size_t)unit * dk;
-    n = dk; turned = rot; freq = freq_k;
-  } else {
-    if (!slots) return;
+  for (int i = threadIdx.x; i < hk + hv; i += blockDim.x) {
+    float c, s;
+    if (i < hk) { pa_sincos(p, freq_k, i, c, s); cs_k[2 * i] = c; cs_k[2 * i + 1] = s; }
+    else { pa_sincos(p, freq_v, i - hk, c, s); cs_v[2 * (i - hk)] = c; cs_v[2 * (i - hk) + 1] = s; }
+  }
+  __syncthreads();
+  const float* row = proj + t * ld;
+  size_t k_at = 0, v_at = 0;
+  if (slots) {
     const int slot = slots[t];
     const size_t page = slot / page_size, off = slot % page_size;
-    if (unit < H + G) {
-      const int g = unit - H;
-      src = proj + t * ld + (size_t)H * dk + (size_t)g * dk;
-      dst = k_cache + ((page * G + g) * page_size + off) * dk;
-      n = dk; turned = rot; freq = freq_k;
+    k_at = (page * G * page_size + off) * dk;      // + g * page_size * dk
+    v_at = (page * G * page_size + off) * dv;
+  }
+  // queries and keys: per head dk - hk items (a pair, or a channel that does not turn)
+  const int per_qk = dk - hk, units_qk = H + (slots ? G : 0);
+  for (int e = threadIdx.x; e < units_qk * per_qk; e += blockDim.x) {
+    const int u = e / per_qk, i = e - u * per_qk;
+    const float* src = row + (size_t)u * dk;
+    TT* dst = u < H ? q_out + t * ldq + (size_t)u * dk : k_cache + k_at + (size_t)(u - H) * page_size * dk;
+    if (i < hk) {
+      const float c = cs_k[2 * i], s = cs_k[2 * i + 1];
+      const float a = src[i], b = src[i + hk];
+      dst[i] = co_from_float<TT>(a * c - b * s);
+      dst[i + hk] = co_from_float<TT>(b * c + a * s);
     } else {
-      const int g = unit - H - G;
-      src = proj + t * ld + (size_t)(H + G) * dk + (size_t)g * dv;
-      dst = v_cache + ((page * G + g) * page_size + off) * dv;
-      n = dv; turned = freq_v ? dv : 0; freq = freq_v;
+      dst[i + hk] = co_from_float<TT>(src[i + hk]);
     }
   }
-  const int half = turned / 2;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    float c, s;
-    pa_sincos(p, freq, i, c, s);
-    const float a = src[i], b = src[i + half];
-    dst[i] = co_from_float<TT>(a * c - b * s);
-    dst[i + half] = co_from_float<TT>(b * c + a * s);
+  if (!slots) return;
+  const int per_v = dv - hv;
+  const float* vrow = row + (size_t)(H + G) * dk;
+  for (int e = threadIdx.x; e < G * per_v; e += blockDim.x) {
+    const int u = e / per_v, i = e - u * per_v;
+    const float* src = vrow + (size_t)u * dv;
+    TT* dst = v_cache + v_at + (size_t)u * page_size * dv;
+    if (i < hv) {
+      const float c = cs_v[2 * i], s = cs_v[2 * i + 1];
+      const float a = src[i], b = src[i + hv];
+      dst[i] = co_from_float<TT>(a * c - b * s);
+      dst[i + hv] = co_from_float<TT>(b * c + a * s);
+    } else {
+      dst[i + hv] = co_from_float<TT>(src[i + hv]);
+    }
   }
-  for (int i = turned + threadIdx.x; i < n; i += blockDim.x) dst[i] = co_from_float<TT>(src[i]);
 }
 
 // grid (B * per_request, G): candidate `which` of request r is block first + which, first = the first block whose last
@@ -277,6 +293,193 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_kernel(AttnArg
   }
 }
 
+// The same attention with the query heads of a key head side by side: one CTA per (row, key head) reads every cached row
+// once for all HPG heads that share it.  NPL: channels per lane (4: head sizes up to 128; 8: up to 256).  With head sizes
+// in multiples of 128 a lane holds four neighbouring channels (one 8- or 16-byte access), else channels 32 apart.
+template <typename TT, int NPL>
+__device__ __forceinline__ void pa_load_row(const TT* row, int n, bool vec, int lane, float (&out)[NPL]) {
+  if (vec) {
+#pragma unroll
+    for (int e4 = 0; e4 < NPL / 4; ++e4) {
+      const int c = e4 * 128 + 4 * lane;
+      if (c < n) {
+        if constexpr (sizeof(TT) == 2) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(row + c);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          out[4 * e4] = __bfloat162float(lo.x); out[4 * e4 + 1] = __bfloat162float(lo.y);
+          out[4 * e4 + 2] = __bfloat162float(hi.x); out[4 * e4 + 3] = __bfloat162float(hi.y);
+        } else {
+          const float4 raw = *reinterpret_cast<const float4*>(row + c);
+          out[4 * e4] = raw.x; out[4 * e4 + 1] = raw.y; out[4 * e4 + 2] = raw.z; out[4 * e4 + 3] = raw.w;
+        }
+      } else {
+        out[4 * e4] = out[4 * e4 + 1] = out[4 * e4 + 2] = out[4 * e4 + 3] = 0.f;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < NPL; ++e) {
+      const int c = lane + 32 * e;
+      out[e] = c < n ? co_to_float<TT>(row[c]) : 0.f;
+    }
+  }
+}
+__device__ __forceinline__ int pa_channel(int e, int lane, bool vec) { return vec ? (e >> 2) * 128 + 4 * lane + (e & 3) : lane + 32 * e; }
+
+template <typename TT, int HPG, int NPL>
+__global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_group_kernel(AttnArgs A) {
+  extern __shared__ __align__(16) float sm[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  const int g = blockIdx.y, h0 = g * HPG;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int dk = A.dk, dv = A.dv;
+  const bool vec = (dk % 128 == 0) && (dv % 128 == 0);
+  float* acc_s = sm;                               // [PA_WARPS][HPG][dv]
+  float* ml = acc_s + PA_WARPS * HPG * dv;         // [PA_WARPS][HPG][2]
+  float* os = ml + 2 * PA_WARPS * HPG;             // [HPG][dv]
+  const int i = A.positions[t];
+  const int r = A.token_req[t];
+  const int* table = A.tables + (size_t)r * A.table_width;
+  const int lo = A.window > 0 ? max(0, i - A.window + 1) : 0;
+  const int nb = (A.pool > 0 && A.window > 0 && i - A.window + 1 > 0) ? (i - A.window + 1) / A.pool : 0;
+  const int total = nb + (i - lo + 1);
+  float qreg[HPG][NPL], acc[HPG][NPL], m[HPG], l[HPG], mult[HPG];
+#pragma unroll
+  for (int hh = 0; hh < HPG; ++hh) {
+    pa_load_row<TT, NPL>((const TT*)A.q + t * A.ldq + (size_t)(h0 + hh) * dk, dk, vec, lane, qreg[hh]);
+    mult[hh] = A.scale * (A.temps ? A.temps[h0 + hh] : 1.f);
+    m[hh] = -INFINITY; l[hh] = 0.f;
+#pragma unroll
+    for (int e = 0; e < NPL; ++e) acc[hh][e] = 0.f;
+  }
+  for (int n0 = warp * PA_KEYS; n0 < total; n0 += PA_WARPS * PA_KEYS) {
+    float kv[PA_KEYS][NPL], vv[PA_KEYS][NPL];
+#pragma unroll
+    for (int b = 0; b < PA_KEYS; ++b) {
+      const int n = min(n0 + b, total - 1);
+      const TT* kr;
+      const TT* vr;
+      if (n < nb) {
+        const long last = (long)n * A.pool + A.pool - 1;
+        const int lp = (int)(last / A.page_size);
+        const int row = n - (int)(((long)lp * A.page_size) / A.pool);
+        const size_t at = ((size_t)A.pool_tables[(size_t)r * A.pool_table_width + lp] * A.G + g) * A.pool_rows + row;
+        kr = (const TT*)A.pk + at * dk;
+        vr = (const TT*)A.pv + at * dv;
+      } else {
+        const int pos = lo + (n - nb);
+        const size_t at = ((size_t)table[pos / A.page_size] * A.G + g) * A.page_size + (size_t)(pos % A.page_size);
+        kr = (const TT*)A.k + at * dk;
+        vr = (const TT*)A.v + at * dv;
+      }
+      pa_load_row<TT, NPL>(kr, dk, vec, lane, kv[b]);
+      pa_load_row<TT, NPL>(vr, dv, vec, lane, vv[b]);
+    }
+#pragma unroll
+    for (int hh = 0; hh < HPG; ++hh) {
+      float s[PA_KEYS];
+      float m_new = m[hh];
+#pragma unroll
+      for (int b = 0; b < PA_KEYS; ++b) {
+        float x = 0.f;
+#pragma unroll
+        for (int e = 0; e < NPL; ++e) x = fmaf(qreg[hh][e], kv[b][e], x);
+        x = co_warp_sum(x) * mult[hh];
+        if (A.cap > 0.f) x = A.cap * tanhf(x / A.cap);
+        s[b] = n0 + b < total ? x : -INFINITY;
+        m_new = fmaxf(m_new, s[b]);
+      }
+      const float f = expf(m[hh] - m_new);
+      l[hh] *= f;
+#pragma unroll
+      for (int e = 0; e < NPL; ++e) acc[hh][e] *= f;
+#pragma unroll
+      for (int b = 0; b < PA_KEYS; ++b) {
+        const float w = expf(s[b] - m_new);
+        l[hh] += w;
+#pragma unroll
+        for (int e = 0; e < NPL; ++e) acc[hh][e] = fmaf(w, vv[b][e], acc[hh][e]);
+      }
+      m[hh] = m_new;
+    }
+  }
+#pragma unroll
+  for (int hh = 0; hh < HPG; ++hh) {
+#pragma unroll
+    for (int e = 0; e < NPL; ++e) {
+      const int c = pa_channel(e, lane, vec);
+      if (c < dv) acc_s[(warp * HPG + hh) * dv + c] = acc[hh][e];
+    }
+    if (lane == 0) { ml[2 * (warp * HPG + hh)] = m[hh]; ml[2 * (warp * HPG + hh) + 1] = l[hh]; }
+  }
+  __syncthreads();
+  // merge in warp order; the sink joins the denominator once
+  for (int e = threadIdx.x; e < HPG * dv; e += blockDim.x) {
+    const int hh = e / dv, c = e - hh * dv;
+    const float sk = A.sinks ? A.sinks[h0 + hh] : -INFINITY;
+    float top = sk;
+#pragma unroll
+    for (int w = 0; w < PA_WARPS; ++w) top = fmaxf(top, ml[2 * (w * HPG + hh)]);
+    float denom = A.sinks ? expf(sk - top) : 0.f;
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < PA_WARPS; ++w) {
+      const float mw = ml[2 * (w * HPG + hh)];
+      const float fw = mw == -INFINITY ? 0.f : expf(mw - top);
+      denom += ml[2 * (w * HPG + hh) + 1] * fw;
+      o = fmaf(acc_s[(w * HPG + hh) * dv + c], fw, o);
+    }
+    os[e] = o / denom;
+  }
+  __syncthreads();
+  const int half = dv / 2;
+  const float p = (float)i;
+  for (int e = threadIdx.x; e < HPG * (A.freq_v ? half : dv); e += blockDim.x) {
+    if (A.freq_v) {
+      const int hh = e / half, c = e - hh * half;
+      TT* out = (TT*)A.out + t * A.ldo + (size_t)(h0 + hh) * dv;
+      const float* gate = A.gates ? A.gates + t * A.ldgate + (size_t)(h0 + hh) * dv : nullptr;
+      float cs, sn;
+      pa_sincos(p, A.freq_v, c, cs, sn);
+      const float a = os[hh * dv + c], b = os[hh * dv + c + half];
+      float x0 = a * cs + b * sn, x1 = b * cs - a * sn;        // turned by -p
+      if (gate) {
+        x0 *= 1.0f / (1.0f + expf(-gate[c]));
+        x1 *= 1.0f / (1.0f + expf(-gate[c + half]));
+      }
+      out[c] = co_from_float<TT>(x0);
+      out[c + half] = co_from_float<TT>(x1);
+    } else {
+      const int hh = e / dv, c = e - hh * dv;
+      float x = os[e];
+      if (A.gates) x *= 1.0f / (1.0f + expf(-A.gates[t * A.ldgate + (size_t)(h0 + hh) * dv + c]));
+      ((TT*)A.out)[t * A.ldo + (size_t)(h0 + hh) * dv + c] = co_from_float<TT>(x);
+    }
+  }
+}
+
+template <typename TT>
+static bool launch_grouped(const AttnArgs& A, int T, cudaStream_t stream) {
+  const int hpg = A.H / A.G, big = max(A.dk, A.dv);
+  const int npl = big <= 128 ? 4 : 8;
+  if (hpg * npl > 32 || (hpg != 1 && hpg != 2 && hpg != 4 && hpg != 8)) return false;
+  const size_t smem = (size_t)(PA_WARPS * hpg * A.dv + 2 * PA_WARPS * hpg + hpg * A.dv) * sizeof(float);
+  if (smem > 48 * 1024) return false;
+  // rows whose accesses are vectors must start on vector boundaries
+  if (A.dk % 128 == 0 && A.dv % 128 == 0 && ((A.ldq * sizeof(TT)) % 16 || ((uintptr_t)A.q & 15))) return false;
+  dim3 grid(T, A.G), block(PA_WARPS * 32);
+#define GO(HPG, NPL) co_launch(pooled_attention_group_kernel<TT, HPG, NPL>, grid, block, smem, stream, A)
+  if (npl == 4) {
+    if (hpg == 1) GO(1, 4); else if (hpg == 2) GO(2, 4); else if (hpg == 4) GO(4, 4); else GO(8, 4);
+  } else {
+    if (hpg == 1) GO(1, 8); else if (hpg == 2) GO(2, 8); else GO(4, 8);
+  }
+#undef GO
+  return true;
+}
+
 }  // namespace
 
 CO_EXPORT int coheryn_pooled_prepare(const float* proj, long ld, const int* positions, const float* freq_k, int rot,
@@ -286,13 +489,14 @@ CO_EXPORT int coheryn_pooled_prepare(const float* proj, long ld, const int* posi
   if (rot < 0 || rot > dk || (rot & 1)) CO_FAIL("pooled_prepare: %d rotated channels of %d", rot, dk);
   if (rot && !freq_k) CO_FAIL("pooled_prepare: a rotation needs frequencies");
   if (freq_v && (dv & 1)) CO_FAIL("pooled_prepare: rotated values need an even number of channels, not %d", dv);
-  dim3 grid(T, H + (slots ? 2 * G : 0));
-  const int threads = 64;
+  dim3 grid(T);
+  const int threads = 256;
+  const size_t smem = (size_t)(rot + (freq_v ? dv : 0)) * sizeof(float);
   if (dtype == CO_F32)
-    co_launch(pooled_prepare_kernel<float>, grid, dim3(threads), 0, stream, proj, ld, positions, freq_k, rot, freq_v, (float*)q_out, ldq,
+    co_launch(pooled_prepare_kernel<float>, grid, dim3(threads), smem, stream, proj, ld, positions, freq_k, rot, freq_v, (float*)q_out, ldq,
               slots, (float*)k_cache, (float*)v_cache, H, G, dk, dv, page_size);
   else if (dtype == CO_BF16)
-    co_launch(pooled_prepare_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, proj, ld, positions, freq_k, rot, freq_v,
+    co_launch(pooled_prepare_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream, proj, ld, positions, freq_k, rot, freq_v,
               (__nv_bfloat16*)q_out, ldq, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, G, dk, dv, page_size);
   else CO_FAIL("pooled_prepare: unknown dtype %d", dtype);
   CO_CHECK_LAUNCH("pooled_prepare");
@@ -332,10 +536,15 @@ CO_EXPORT int coheryn_pooled_attention(const void* q, long ldq, void* out, long 
   if (pool > 0 && (!pk || !pv || !pool_tables)) CO_FAIL("pooled_attention: blocks need their cache");
   AttnArgs A{q, ldq, out, ldo, k, v, pk, pv, tables, table_width, pool_tables, pool_table_width, token_req, positions, temps, sinks,
              gates, ldgate, freq_v, H, G, dk, dv, page_size, window, pool, pool_rows, scale, cap};
+  if (dtype != CO_F32 && dtype != CO_BF16) CO_FAIL("pooled_attention: unknown dtype %d", dtype);
+  static const bool grouped = !(getenv("COHERYN_POOLED_GROUPED") && getenv("COHERYN_POOLED_GROUPED")[0] == '0');
+  if (grouped && (dtype == CO_F32 ? launch_grouped<float>(A, T, stream) : launch_grouped<__nv_bfloat16>(A, T, stream))) {
+    CO_CHECK_LAUNCH("pooled_attention_group");
+    return 0;
+  }
   const size_t smem = (size_t)(dk + (PA_WARPS + 1) * dv + 2 * PA_WARPS) * sizeof(float);
   if (dtype == CO_F32) co_launch(pooled_attention_kernel<float>, dim3(T, H), dim3(PA_WARPS * 32), smem, stream, A);
-  else if (dtype == CO_BF16) co_launch(pooled_attention_kernel<__nv_bfloat16>, dim3(T, H), dim3(PA_WARPS * 32), smem, stream, A);
-  else CO_FAIL("pooled_attention: unknown dtype %d", dtype);
+  else co_launch(pooled_attention_kernel<__nv_bfloat16>, dim3(T, H), dim3(PA_WARPS * 32), smem, stream, A);
   CO_CHECK_LAUNCH("pooled_attention");
   return 0;
 }

@@ -30,6 +30,7 @@ namespace {
 
 constexpr int DK = CO_PW_DK, DV = CO_PW_DV;
 constexpr int BM = 64, BN = 64, WARPS = 4;
+constexpr float LOG2E = 1.4426950408889634f;
 constexpr int LDK = DK + 8, LDV = DV + 8;          // shared-memory row strides (elements): no bank conflicts for ldmatrix
 static_assert(DK % 16 == 0 && DV % 16 == 0 && DK <= 256 && DV <= 128, "head sizes the tensor-core kernel takes");
 
@@ -121,29 +122,34 @@ __global__ void __launch_bounds__(WARPS * 32) pooled_attention_tc_kernel(TcArgs 
     __nv_bfloat16* vs = Vs + (size_t)stage * BN * LDV;
     const bool pooled = t < n_pool_tiles;
     const int first = pooled ? t * BN : pos_lo + (t - n_pool_tiles) * BN;
-    constexpr int KC = DK / 8, VC = DV / 8;             // 16-byte chunks per row
-    for (int e = tid; e < BN * (KC + VC); e += WARPS * 32) {
-      const int row = e / (KC + VC), c = e % (KC + VC);
-      const int idx = first + row;
-      const __nv_bfloat16* src;
-      bool valid;
-      size_t at;
-      if (pooled) {
-        valid = idx < nb_max;
-        const int b = valid ? idx : 0;
-        const long last = (long)b * A.pool + A.pool - 1;
-        const int lp = (int)(last / A.page_size);
-        const int prow = b - (int)(((long)lp * A.page_size) / A.pool);
-        at = ((size_t)ptable[lp] * A.G + g) * A.pool_rows + prow;
-        src = c < KC ? A.pk + at * DK + c * 8 : A.pv + at * DV + (c - KC) * 8;
-      } else {
-        valid = idx <= p_last;
-        const int pos = valid ? idx : p_last;
-        at = ((size_t)table[pos / A.page_size] * A.G + g) * A.page_size + (size_t)(pos % A.page_size);
-        src = c < KC ? A.k + at * DK + c * 8 : A.v + at * DV + (c - KC) * 8;
-      }
-      void* dst = c < KC ? (void*)(ks + row * LDK + c * 8) : (void*)(vs + row * LDV + (c - KC) * 8);
-      cp_async16(dst, src, valid);
+    // two threads per key row: one copies its key channels, the other its value channels (the row is looked up once)
+    static_assert(BN * 2 == WARPS * 32, "a thread per (row, keys or values)");
+    const int row = tid >> 1, is_v = tid & 1;
+    const int idx = first + row;
+    bool valid;
+    size_t at;
+    if (pooled) {
+      valid = idx < nb_max;
+      const int b = valid ? idx : 0;
+      const long last = (long)b * A.pool + A.pool - 1;
+      const int lp = (int)(last / A.page_size);
+      const int prow = b - (int)(((long)lp * A.page_size) / A.pool);
+      at = ((size_t)ptable[lp] * A.G + g) * A.pool_rows + prow;
+    } else {
+      valid = idx <= p_last;
+      const int pos = valid ? idx : p_last;
+      at = ((size_t)table[pos / A.page_size] * A.G + g) * A.page_size + (size_t)(pos % A.page_size);
+    }
+    if (is_v) {
+      const __nv_bfloat16* src = (pooled ? A.pv : A.v) + at * DV;
+      __nv_bfloat16* dst = vs + row * LDV;
+#pragma unroll
+      for (int c = 0; c < DV / 8; ++c) cp_async16(dst + c * 8, src + c * 8, valid);
+    } else {
+      const __nv_bfloat16* src = (pooled ? A.pk : A.k) + at * DK;
+      __nv_bfloat16* dst = ks + row * LDK;
+#pragma unroll
+      for (int c = 0; c < DK / 8; ++c) cp_async16(dst + c * 8, src + c * 8, valid);
     }
   };
 
@@ -171,7 +177,6 @@ __global__ void __launch_bounds__(WARPS * 32) pooled_attention_tc_kernel(TcArgs 
 #pragma unroll
   for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float ma = -INFINITY, mb = -INFINITY, la = 0.f, lb = 0.f;
-  constexpr float LOG2E = 1.4426950408889634f;
 
   for (int t = 0; t < n_tiles; ++t) {
     const int stage = t & 1;
@@ -211,23 +216,43 @@ __global__ void __launch_bounds__(WARPS * 32) pooled_attention_tc_kernel(TcArgs 
           mma_bf16(s[2 * np + 1], a, b[2], b[3]);
         }
       }
-      // scale, cap, mask; row maxima
+      // scale, cap, mask; row maxima.  A tile whose every key every row of the warp sees needs no mask.
+      bool inner;
+      {
+        const int wa = p_first + warp * 16, wb = wa + 15;
+        if (pooled) inner = first + BN <= ((wa - A.window + 1 > 0) ? (wa - A.window + 1) / A.pool : 0);
+        else inner = first + BN - 1 <= wa && (A.window <= 0 || first >= wb - A.window + 1);
+      }
       float ta = -INFINITY, tb = -INFINITY;
+      const float two_inv_cap = 2.0f * inv_cap * LOG2E;
 #pragma unroll
       for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int idx = first + n * 8 + 2 * ti + (e & 1);
-          const bool second = e >= 2;
           float x = s[n][e] * mult;
-          if (A.cap > 0.f) x = A.cap * tanhf(x * inv_cap);
-          bool seen;
-          if (pooled) seen = idx < (second ? nbb : nba);
-          else seen = second ? (idx <= ib && idx >= lob) : (idx <= ia && idx >= loa);
-          x = seen ? x : -INFINITY;
+          // cap tanh(x / cap) = cap (1 - 2 / (exp(2 x / cap) + 1)): absolute error a few 1e-7 of the cap
+          if (A.cap > 0.f) x = A.cap - __fdividef(2.0f * A.cap, exp2f(x * two_inv_cap) + 1.0f);
           s[n][e] = x;
-          if (second) tb = fmaxf(tb, x); else ta = fmaxf(ta, x);
         }
+      }
+      if (!inner) {
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int idx = first + n * 8 + 2 * ti + (e & 1);
+            const bool second = e >= 2;
+            bool seen;
+            if (pooled) seen = idx < (second ? nbb : nba);
+            else seen = second ? (idx <= ib && idx >= lob) : (idx <= ia && idx >= loa);
+            if (!seen) s[n][e] = -INFINITY;
+          }
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < BN / 8; ++n) {
+        ta = fmaxf(ta, fmaxf(s[n][0], s[n][1]));
+        tb = fmaxf(tb, fmaxf(s[n][2], s[n][3]));
       }
       ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)); ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
       tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
