@@ -141,6 +141,7 @@ struct AttnArgs {
   const float* freq_v;
   int H, G, dk, dv, page_size, window, pool, pool_rows;
   float scale, cap;
+  int table_room;       // block-table entries that the kernel may keep in shared memory (the pages of a window)
 };
 
 constexpr int PA_WARPS = 8;
@@ -294,7 +295,7 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_kernel(AttnArg
 }
 
 // The same attention with the query heads of a key head side by side: one CTA per (row, key head) reads every cached row
-// once for all HPG heads that share it.  NPL: channels per lane (4: head sizes up to 128; 8: up to 256).  With head sizes
+// once for all HPG heads that share it (1, 2 or 4).  NPL: channels per lane (4: head sizes up to 128).  With head sizes
 // in multiples of 128 a lane holds four neighbouring channels (one 8- or 16-byte access), else channels 32 apart.
 template <typename TT, int NPL>
 __device__ __forceinline__ void pa_load_row(const TT* row, int n, bool vec, int lane, float (&out)[NPL]) {
@@ -326,8 +327,9 @@ __device__ __forceinline__ void pa_load_row(const TT* row, int n, bool vec, int 
 }
 __device__ __forceinline__ int pa_channel(int e, int lane, bool vec) { return vec ? (e >> 2) * 128 + 4 * lane + (e & 3) : lane + 32 * e; }
 
+constexpr int PG_WARPS = 16;         // warps of the kernel that shares cached rows among the heads of a key head
 template <typename TT, int HPG, int NPL>
-__global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_group_kernel(AttnArgs A) {
+__global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(AttnArgs A) {
   extern __shared__ __align__(16) float sm[];
   co_pdl_launch_dependents();
   co_pdl_wait();
@@ -336,26 +338,32 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_group_kernel(A
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int dk = A.dk, dv = A.dv;
   const bool vec = (dk % 128 == 0) && (dv % 128 == 0);
-  float* acc_s = sm;                               // [PA_WARPS][HPG][dv]
-  float* ml = acc_s + PA_WARPS * HPG * dv;         // [PA_WARPS][HPG][2]
-  float* os = ml + 2 * PA_WARPS * HPG;             // [HPG][dv]
+  float* acc_s = sm;                               // [PG_WARPS][HPG][dv]
+  float* ml = acc_s + PG_WARPS * HPG * dv;         // [PG_WARPS][HPG][2]
+  float* os = ml + 2 * PG_WARPS * HPG;             // [HPG][dv]
+  int* table_s = reinterpret_cast<int*>(os + HPG * dv);     // [table_room]
   const int i = A.positions[t];
   const int r = A.token_req[t];
   const int* table = A.tables + (size_t)r * A.table_width;
   const int lo = A.window > 0 ? max(0, i - A.window + 1) : 0;
+  // the pages of the window, looked up once: a warp that waits for a table entry cannot issue anything else meanwhile
+  const int page_lo = lo / A.page_size;
+  const bool staged = i / A.page_size - page_lo < A.table_room;
+  if (staged) {
+    for (int e = threadIdx.x; e <= i / A.page_size - page_lo; e += blockDim.x) table_s[e] = table[page_lo + e];
+    __syncthreads();
+  }
   const int nb = (A.pool > 0 && A.window > 0 && i - A.window + 1 > 0) ? (i - A.window + 1) / A.pool : 0;
   const int total = nb + (i - lo + 1);
-  float qreg[HPG][NPL], acc[HPG][NPL], m[HPG], l[HPG], mult[HPG];
+  float qreg[HPG][NPL], acc[HPG][NPL];
 #pragma unroll
   for (int hh = 0; hh < HPG; ++hh) {
     pa_load_row<TT, NPL>((const TT*)A.q + t * A.ldq + (size_t)(h0 + hh) * dk, dk, vec, lane, qreg[hh]);
-    mult[hh] = A.scale * (A.temps ? A.temps[h0 + hh] : 1.f);
-    m[hh] = -INFINITY; l[hh] = 0.f;
 #pragma unroll
     for (int e = 0; e < NPL; ++e) acc[hh][e] = 0.f;
   }
-  for (int n0 = warp * PA_KEYS; n0 < total; n0 += PA_WARPS * PA_KEYS) {
-    float kv[PA_KEYS][NPL], vv[PA_KEYS][NPL];
+  // the rows of the warp's next keys are requested before the current ones are used (two sets of registers in turn)
+  auto fetch = [&](int n0, float (&kv)[PA_KEYS][NPL], float (&vv)[PA_KEYS][NPL]) {
 #pragma unroll
     for (int b = 0; b < PA_KEYS; ++b) {
       const int n = min(n0 + b, total - 1);
@@ -370,39 +378,102 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_group_kernel(A
         vr = (const TT*)A.pv + at * dv;
       } else {
         const int pos = lo + (n - nb);
-        const size_t at = ((size_t)table[pos / A.page_size] * A.G + g) * A.page_size + (size_t)(pos % A.page_size);
+        const int pi = pos / A.page_size;
+        const size_t page = (size_t)(staged ? table_s[pi - page_lo] : table[pi]);
+        const size_t at = (page * A.G + g) * A.page_size + (size_t)(pos - pi * A.page_size);
         kr = (const TT*)A.k + at * dk;
         vr = (const TT*)A.v + at * dv;
       }
       pa_load_row<TT, NPL>(kr, dk, vec, lane, kv[b]);
       pa_load_row<TT, NPL>(vr, dv, vec, lane, vv[b]);
     }
+  };
+  // The scores of an iteration, NS = HPG x PA_KEYS of them, are summed over the lanes so that each ends up in ONE lane
+  // (a pair of lanes): cap, exponentials and the running maximum are then computed once per score instead of in all 32
+  // lanes, and the weights come back by shuffles.  Score (head hh, key b) has index hh * PA_KEYS + b; bit r of the index is
+  // bit 4 - r of the lanes that hold it.
+  constexpr int NS = HPG * PA_KEYS;
+  constexpr int LOGN = NS == 4 ? 2 : NS == 8 ? 3 : 4;
+  static_assert(NS == 4 || NS == 8 || NS == 16, "four, eight or sixteen scores per iteration");
+  int my_idx = 0;
+#pragma unroll
+  for (int rr = 0; rr < LOGN; ++rr) my_idx |= ((lane >> (4 - rr)) & 1) << rr;
+  const int my_h = my_idx / PA_KEYS, my_b = my_idx % PA_KEYS;
+  const float my_mult = A.scale * (A.temps ? A.temps[h0 + my_h] : 1.f);
+  float my_m = -INFINITY, my_l = 0.f;          // of head my_h (the lanes of a head agree)
+  const float inv_cap = A.cap > 0.f ? 1.0f / A.cap : 0.f;
+  auto source = [](int idx) {
+    int src = 0;
+#pragma unroll
+    for (int rr = 0; rr < LOGN; ++rr) src |= ((idx >> rr) & 1) << (4 - rr);
+    return src;
+  };
+  auto use = [&](int n0, const float (&kv)[PA_KEYS][NPL], const float (&vv)[PA_KEYS][NPL]) {
+    float v[NS];
 #pragma unroll
     for (int hh = 0; hh < HPG; ++hh) {
-      float s[PA_KEYS];
-      float m_new = m[hh];
 #pragma unroll
       for (int b = 0; b < PA_KEYS; ++b) {
         float x = 0.f;
 #pragma unroll
         for (int e = 0; e < NPL; ++e) x = fmaf(qreg[hh][e], kv[b][e], x);
-        x = co_warp_sum(x) * mult[hh];
-        if (A.cap > 0.f) x = A.cap * tanhf(x / A.cap);
-        s[b] = n0 + b < total ? x : -INFINITY;
-        m_new = fmaxf(m_new, s[b]);
+        v[hh * PA_KEYS + b] = x;
       }
-      const float f = expf(m[hh] - m_new);
-      l[hh] *= f;
+    }
+    int off = 16;
+#pragma unroll
+    for (int cnt = NS; cnt > 1; cnt >>= 1) {
+      const bool up = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < cnt / 2; ++i) {
+        const float keep = up ? v[2 * i + 1] : v[2 * i];
+        const float send = up ? v[2 * i] : v[2 * i + 1];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+      off >>= 1;
+    }
+#pragma unroll
+    for (int o2 = 16 >> LOGN; o2 > 0; o2 >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o2);
+    float x = v[0] * my_mult;
+    if (A.cap > 0.f) x = A.cap * tanhf(x * inv_cap);
+    if (n0 + my_b >= total) x = -INFINITY;
+    // the head's keys of this iteration sit in the lanes that differ in bits 4 and 3
+    float top = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 16));
+    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 8));
+    const float m_new = fmaxf(my_m, top);          // finite: the iteration's first key exists
+    const float my_f = expf(my_m - m_new);
+    const float my_w = expf(x - m_new);
+    float sum = my_w + __shfl_xor_sync(0xffffffffu, my_w, 16);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+    my_l = my_l * my_f + sum;
+    my_m = m_new;
+#pragma unroll
+    for (int hh = 0; hh < HPG; ++hh) {
+      const float f = __shfl_sync(0xffffffffu, my_f, source(hh * PA_KEYS));
 #pragma unroll
       for (int e = 0; e < NPL; ++e) acc[hh][e] *= f;
 #pragma unroll
       for (int b = 0; b < PA_KEYS; ++b) {
-        const float w = expf(s[b] - m_new);
-        l[hh] += w;
+        const float w = __shfl_sync(0xffffffffu, my_w, source(hh * PA_KEYS + b));
 #pragma unroll
         for (int e = 0; e < NPL; ++e) acc[hh][e] = fmaf(w, vv[b][e], acc[hh][e]);
       }
-      m[hh] = m_new;
+    }
+  };
+  {
+    constexpr int STRIDE = PG_WARPS * PA_KEYS;
+    float ka[PA_KEYS][NPL], va[PA_KEYS][NPL], kb[PA_KEYS][NPL], vb[PA_KEYS][NPL];
+    int n0 = warp * PA_KEYS;
+    if (n0 < total) fetch(n0, ka, va);
+    while (n0 < total) {
+      const int n1 = n0 + STRIDE;
+      if (n1 < total) fetch(n1, kb, vb);
+      use(n0, ka, va);
+      if (n1 >= total) break;
+      const int n2 = n1 + STRIDE;
+      if (n2 < total) fetch(n2, ka, va);
+      use(n1, kb, vb);
+      n0 = n2;
     }
   }
 #pragma unroll
@@ -412,7 +483,10 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_group_kernel(A
       const int c = pa_channel(e, lane, vec);
       if (c < dv) acc_s[(warp * HPG + hh) * dv + c] = acc[hh][e];
     }
-    if (lane == 0) { ml[2 * (warp * HPG + hh)] = m[hh]; ml[2 * (warp * HPG + hh) + 1] = l[hh]; }
+  }
+  if (lane == source(my_h * PA_KEYS)) {        // one lane per head: the one whose unused bits are zero
+    ml[2 * (warp * HPG + my_h)] = my_m;
+    ml[2 * (warp * HPG + my_h) + 1] = my_l;
   }
   __syncthreads();
   // merge in warp order; the sink joins the denominator once
@@ -421,11 +495,11 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_group_kernel(A
     const float sk = A.sinks ? A.sinks[h0 + hh] : -INFINITY;
     float top = sk;
 #pragma unroll
-    for (int w = 0; w < PA_WARPS; ++w) top = fmaxf(top, ml[2 * (w * HPG + hh)]);
+    for (int w = 0; w < PG_WARPS; ++w) top = fmaxf(top, ml[2 * (w * HPG + hh)]);
     float denom = A.sinks ? expf(sk - top) : 0.f;
     float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < PA_WARPS; ++w) {
+    for (int w = 0; w < PG_WARPS; ++w) {
       const float mw = ml[2 * (w * HPG + hh)];
       const float fw = mw == -INFINITY ? 0.f : expf(mw - top);
       denom += ml[2 * (w * HPG + hh) + 1] * fw;
@@ -464,18 +538,20 @@ template <typename TT>
 static bool launch_grouped(const AttnArgs& A, int T, cudaStream_t stream) {
   const int hpg = A.H / A.G, big = max(A.dk, A.dv);
   const int npl = big <= 128 ? 4 : 8;
-  if (hpg * npl > 32 || (hpg != 1 && hpg != 2 && hpg != 4 && hpg != 8)) return false;
-  const size_t smem = (size_t)(PA_WARPS * hpg * A.dv + 2 * PA_WARPS * hpg + hpg * A.dv) * sizeof(float);
-  if (smem > 48 * 1024) return false;
+  // wider heads or more heads per key head do not fit the registers of two sets of rows; they take the kernel per head
+  if (npl != 4 || (hpg != 1 && hpg != 2 && hpg != 4)) return false;
+  const size_t smem = (size_t)(PG_WARPS * hpg * A.dv + 2 * PG_WARPS * hpg + hpg * A.dv + A.table_room) * sizeof(float);
+  if (smem > 96 * 1024) return false;
   // rows whose accesses are vectors must start on vector boundaries
   if (A.dk % 128 == 0 && A.dv % 128 == 0 && ((A.ldq * sizeof(TT)) % 16 || ((uintptr_t)A.q & 15))) return false;
-  dim3 grid(T, A.G), block(PA_WARPS * 32);
-#define GO(HPG, NPL) co_launch(pooled_attention_group_kernel<TT, HPG, NPL>, grid, block, smem, stream, A)
-  if (npl == 4) {
-    if (hpg == 1) GO(1, 4); else if (hpg == 2) GO(2, 4); else if (hpg == 4) GO(4, 4); else GO(8, 4);
-  } else {
-    if (hpg == 1) GO(1, 8); else if (hpg == 2) GO(2, 8); else GO(4, 8);
-  }
+  dim3 grid(T, A.G), block(PG_WARPS * 32);
+#define GO(HPG, NPL)                                                                                                        \
+  do {                                                                                                                      \
+    if (smem > 48 * 1024)                                                                                                   \
+      cudaFuncSetAttribute(pooled_attention_group_kernel<TT, HPG, NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    co_launch(pooled_attention_group_kernel<TT, HPG, NPL>, grid, block, smem, stream, A);                                   \
+  } while (0)
+  if (hpg == 1) GO(1, 4); else if (hpg == 2) GO(2, 4); else GO(4, 4);
 #undef GO
   return true;
 }
@@ -535,7 +611,8 @@ CO_EXPORT int coheryn_pooled_attention(const void* q, long ldq, void* out, long 
     CO_FAIL("pooled_attention: head sizes %d / %d (1..%d)", dk, dv, 32 * PA_MAX_PER_LANE);
   if (pool > 0 && (!pk || !pv || !pool_tables)) CO_FAIL("pooled_attention: blocks need their cache");
   AttnArgs A{q, ldq, out, ldo, k, v, pk, pv, tables, table_width, pool_tables, pool_table_width, token_req, positions, temps, sinks,
-             gates, ldgate, freq_v, H, G, dk, dv, page_size, window, pool, pool_rows, scale, cap};
+             gates, ldgate, freq_v, H, G, dk, dv, page_size, window, pool, pool_rows, scale, cap,
+             window > 0 && window / page_size + 2 <= 2048 ? window / page_size + 2 : 0};
   if (dtype != CO_F32 && dtype != CO_BF16) CO_FAIL("pooled_attention: unknown dtype %d", dtype);
   static const bool grouped = !(getenv("COHERYN_POOLED_GROUPED") && getenv("COHERYN_POOLED_GROUPED")[0] == '0');
   if (grouped && (dtype == CO_F32 ? launch_grouped<float>(A, T, stream) : launch_grouped<__nv_bfloat16>(A, T, stream))) {

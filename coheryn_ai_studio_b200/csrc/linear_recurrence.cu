@@ -85,16 +85,38 @@ struct ScanArgs {
 __device__ __forceinline__ float lr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float lr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// (log a, a - 1, drive) of token t and channel c; sp = rate * softplus(lam[c]).
-__device__ __forceinline__ void lr_coefficients(const ScanArgs& A, int t, int c, float sp, float b_r, float b_i, float& log_a,
-                                                float& am1, float& d) {
+// What a token brings for channel c: the gates' pre-activations, the input, the other branch, and whether its request's
+// run begins here (then with the state to start from).
+struct Tok {
+  float zr, zi, u, y, start;
+  int req;
+  bool first;
+};
+constexpr int GROUP = 4;      // tokens whose inputs are requested together, ahead of the chain of multiply-adds
+
+template <bool WITH_Y>
+__device__ __forceinline__ Tok lr_load(const ScanArgs& A, int t, int c, const float* from) {
+  Tok k;
   const int blk = c / A.bs, j = c - blk * A.bs;
   const float* g = A.gates + (size_t)t * A.ldg + (size_t)blk * 2 * A.bs;
-  const float r = lr_sigmoid(g[j] + b_r);
-  const float i = lr_sigmoid(g[A.bs + j] + b_i);
+  k.zr = g[j];
+  k.zi = g[A.bs + j];
+  k.u = A.u[(size_t)t * A.ldu + c];
+  k.y = WITH_Y ? A.y[(size_t)t * A.ldy + c] : 0.f;
+  k.req = A.token_req[t];
+  k.first = t == A.cu_q[k.req];
+  k.start = 0.f;
+  if (k.first) k.start = from ? from[(size_t)k.req * A.C + c] : A.state[(size_t)A.state_slots[k.req] * A.state_stride + c];
+  return k;
+}
+
+// (log a, a - 1, drive); sp = rate * softplus(lam[c]).
+__device__ __forceinline__ void lr_coefficients(const Tok& k, float sp, float b_r, float b_i, float& log_a, float& am1, float& d) {
+  const float r = lr_sigmoid(k.zr + b_r);
+  const float i = lr_sigmoid(k.zi + b_i);
   log_a = -sp * r;
   am1 = expm1f(log_a);
-  d = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f)) * i * A.u[(size_t)t * A.ldu + c];
+  d = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f)) * i * k.u;
 }
 
 __global__ void __launch_bounds__(LANES) scan_summaries_kernel(ScanArgs A) {
@@ -107,17 +129,24 @@ __global__ void __launch_bounds__(LANES) scan_summaries_kernel(ScanArgs A) {
   co_pdl_wait();
   const int t0 = chunk * CHUNK, t1 = min(t0 + CHUNK, A.T);
   float logs = 0.f, S = 0.f;
-  for (int t = t0; t < t1; ++t) {
-    const int r = A.token_req[t];
-    if (t == A.cu_q[r]) {        // a request's run begins: what came before does not reach beyond this token
-      S = A.state[(size_t)A.state_slots[r] * A.state_stride + c];
-      A.first[(size_t)r * A.C + c] = S;
-      logs = -INFINITY;
+  for (int tg = t0; tg < t1; tg += GROUP) {
+    Tok k[GROUP];
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j)
+      if (tg + j < t1) k[j] = lr_load<false>(A, tg + j, c, nullptr);
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) {
+      if (tg + j >= t1) break;
+      if (k[j].first) {        // a request's run begins: what came before does not reach beyond this token
+        S = k[j].start;
+        A.first[(size_t)k[j].req * A.C + c] = S;
+        logs = -INFINITY;
+      }
+      float log_a, am1, d;
+      lr_coefficients(k[j], sp, b_r, b_i, log_a, am1, d);
+      S = fmaf(am1, S, S) + d;
+      logs += log_a;
     }
-    float log_a, am1, d;
-    lr_coefficients(A, t, c, sp, b_r, b_i, log_a, am1, d);
-    S = fmaf(am1, S, S) + d;
-    logs += log_a;
   }
   A.carry_a[(size_t)chunk * A.C + c] = logs;
   A.carry_s[(size_t)chunk * A.C + c] = S;
@@ -146,14 +175,22 @@ __global__ void __launch_bounds__(LANES) scan_outputs_kernel(ScanArgs A) {
     }
   }
   TO* out = (TO*)A.out;
-  for (int t = t0; t < t1; ++t) {
-    const int r = A.token_req[t];
-    if (t == A.cu_q[r]) S = A.first[(size_t)r * A.C + c];
-    float log_a, am1, d;
-    lr_coefficients(A, t, c, sp, b_r, b_i, log_a, am1, d);
-    S = fmaf(am1, S, S) + d;
-    out[(size_t)t * A.ldo + c] = co_from_float<TO>(S * co_gelu_tanh(A.y[(size_t)t * A.ldy + c]));
-    if (t + 1 == A.cu_q[r + 1]) A.state[(size_t)A.state_slots[r] * A.state_stride + c] = S;
+  for (int tg = t0; tg < t1; tg += GROUP) {
+    Tok k[GROUP];
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j)
+      if (tg + j < t1) k[j] = lr_load<true>(A, tg + j, c, A.first);
+#pragma unroll
+    for (int j = 0; j < GROUP; ++j) {
+      const int t = tg + j;
+      if (t >= t1) break;
+      if (k[j].first) S = k[j].start;
+      float log_a, am1, d;
+      lr_coefficients(k[j], sp, b_r, b_i, log_a, am1, d);
+      S = fmaf(am1, S, S) + d;
+      out[(size_t)t * A.ldo + c] = co_from_float<TO>(S * co_gelu_tanh(k[j].y));
+      if (t + 1 == A.cu_q[k[j].req + 1]) A.state[(size_t)A.state_slots[k[j].req] * A.state_stride + c] = S;
+    }
   }
 }
 

@@ -667,8 +667,9 @@ class PooledWindowAttention(Mixer):
             raise ValueError("a window attention with block means needs pages for the positions and pages for the blocks")
         return cache.parts[0], cache.parts[1]
 
-    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
-        """The gated heads in front of the output product into ``outs[0]`` [T, heads * vdim]."""
+    def _write(self, x: torch.Tensor, step: StepContext, cache: LayerCache):
+        """Projections of every row; keys and values rotated and cached, the blocks that the step completed averaged.
+        Returns (rotated queries [T, heads * dk], the projections [T, ..] whose last columns are the gate's)."""
         kv, blocks = self._caches(cache)
         if not kv.writes:
             raise ValueError("this attention keeps its own keys and values")
@@ -681,11 +682,22 @@ class PooledWindowAttention(Mixer):
                                kv.page_size, self.runtime.dtype)
         if blocks is not None:
             ops.pooled_means(kv.k, kv.v, blocks.k, blocks.v, step, kv.group, blocks.group, G, dk, dv, kv.page_size, self.pool)
+        return q, proj
+
+    def _attend(self, q: torch.Tensor, proj: torch.Tensor, out: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
+        kv, blocks = self._caches(cache)
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dk, self.dv
+        freq_v = self.value_position.frequency_pairs() if self.value_position is not None else None
         gates = proj[:, H * dk + G * (dk + dv):] if self.gate else None
-        ops.pooled_attention(q, outs[0], kv.k, kv.v, blocks.k if blocks is not None else None,
+        ops.pooled_attention(q, out, kv.k, kv.v, blocks.k if blocks is not None else None,
                              blocks.v if blocks is not None else None, step, kv.group,
                              blocks.group if blocks is not None else None, H, G, dk, dv, kv.page_size, self.window, self.pool,
                              self.scale, self.softcap, self.temps, self.sinks, gates, freq_v)
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
+        """The gated heads in front of the output product into ``outs[0]`` [T, heads * vdim]."""
+        q, proj = self._write(x, step, cache)
+        self._attend(q, proj, outs[0], step, cache)
 
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
         o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
@@ -695,6 +707,19 @@ class PooledWindowAttention(Mixer):
     def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
         o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
         self.forward_open(x, step, cache, [o])
+        return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
+    supports_tail = True
+
+    def forward_tail(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> Optional[torch.Tensor]:
+        """Keys, values and block means of every row go to the cache; only the wanted rows attend, each as a one-token
+        request of ``step.tail`` (the keys they look back on were written by this same step)."""
+        q, proj = self._write(x, step, cache)
+        rows, tail = step.tail_rows, step.tail
+        if not tail.num_tokens:
+            return None
+        o = torch.empty((tail.num_tokens, self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self._attend(ops.gather_rows(q, rows), ops.gather_rows(proj, rows), o, tail, cache)
         return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
 
 

@@ -260,6 +260,16 @@ class GatedLinearRecurrence(_StateMixer):
         self.forward_open(x, step, cache, [o])
         ops.linear(o, self.w_o, out=out[0])
 
+    supports_tail = True
+
+    def forward_tail(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> Optional[torch.Tensor]:
+        """The state passes every row; the output product runs for the wanted rows only."""
+        o = torch.empty((x.shape[0], self.width), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        if not step.tail.num_tokens:
+            return None
+        return ops.linear(ops.gather_rows(o, step.tail_rows), self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
     def forward_open(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], outs) -> None:
         """S * y, the activations in front of the output product, into ``outs[0]`` [T, width]."""
         state = self._state_of(cache)

@@ -505,6 +505,32 @@ def test_batched_rows_equal_the_rows_of_each_request_alone(name, dtype, folders,
         assert d <= (1e-4 if dtype == "float32" else 0.05) * np.std(alone.rows[("a", p)]), (p, d)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_few_wanted_rows_take_the_last_layers_shortcut(name, dtype, folders, models):
+    """Steps that want few rows (or none) run the last layer's attention scores, output products and experts for those rows
+    only (Z1, Z2: a last layer that is a recurrence or an attention without feed-forward; Z3: a window attention with blocks
+    of one): the logits equal the plain implementation's, the cache and the state that later steps read are complete, and
+    switching the shortcut off changes nothing beyond rounding."""
+    n = 131
+    seq, other = zc.prompt(33, n, vocab(name)), zc.prompt(34, 40, vocab(name))
+    runs = {}
+    for shortcut in (True, False):
+        r = zc.noisy_replay(folders[name], dtype, 256, models(name, dtype))
+        r.runner.tail_shortcut = shortcut
+        r.step([("r", seq[:30], [])])
+        r.step([("r", seq[30:60], [29, 3]), ("o", other[:20], [19])])
+        r.step([("r", seq[60:n - 5], [0]), ("o", other[20:], [])])
+        r.step([("r", seq[n - 5:], list(range(5)))])
+        assert set(k for k in r.rows if k[0] == "r") == {("r", p) for p in [59, 33, 60] + list(range(n - 5, n))}
+        zc.check_rows(r.rows, folders[name], {"r": seq, "o": other}, dtype, f"shortcut {shortcut}")
+        runs[shortcut] = r.rows
+    assert models(name, dtype).layers[-1].supports_tail
+    for key, row in runs[True].items():
+        d = np.abs(row - runs[False][key]).max()
+        assert d <= (1e-4 if dtype == "float32" else 0.08 * np.std(row)), (key, d)
+
+
 def test_tensor_core_attention_equals_the_float32_arithmetic_one_in_a_model(folders, models):
     """The same bfloat16 steps with the tensor-core attention switched off: rows agree within rounding."""
     from coheryn_ai_studio_b200 import ops
