@@ -142,6 +142,8 @@ struct AttnArgs {
   int H, G, dk, dv, page_size, window, pool, pool_rows;
   float scale, cap;
   int table_room;       // block-table entries that the kernel may keep in shared memory (the pages of a window)
+  int splits;           // CTAs that share a row's keys (grouped kernel); their parts meet in `scratch`
+  float* scratch;       // [T][G][splits][HPG * dv + 2 * HPG]: unnormalised sums, then (maximum, sum) per head
 };
 
 constexpr int PA_WARPS = 8;
@@ -297,39 +299,54 @@ __global__ void __launch_bounds__(PA_WARPS * 32) pooled_attention_kernel(AttnArg
 // The same attention with the query heads of a key head side by side: one CTA per (row, key head) reads every cached row
 // once for all HPG heads that share it (1, 2 or 4).  NPL: channels per lane (4: head sizes up to 128).  With head sizes
 // in multiples of 128 a lane holds four neighbouring channels (one 8- or 16-byte access), else channels 32 apart.
-template <typename TT, int NPL>
-__device__ __forceinline__ void pa_load_row(const TT* row, int n, bool vec, int lane, float (&out)[NPL]) {
-  if (vec) {
+// A cached row as a lane holds it between the request and its use: the bits as they were loaded (converting them at once
+// would make the warp wait for the load right there, and nothing could be requested ahead).
+template <typename TT> struct Four;
+template <> struct Four<float> {
+  float4 d;
+  __device__ __forceinline__ void load(const float* p) { d = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void zero() { d = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ float get(int j) const { return j == 0 ? d.x : j == 1 ? d.y : j == 2 ? d.z : d.w; }
+};
+template <> struct Four<__nv_bfloat16> {
+  uint2 d;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { d = *reinterpret_cast<const uint2*>(p); }
+  __device__ __forceinline__ void zero() { d = make_uint2(0u, 0u); }
+  __device__ __forceinline__ float get(int j) const {
+    const unsigned w = j < 2 ? d.x : d.y;
+    return __uint_as_float((j & 1) ? (w & 0xffff0000u) : (w << 16));
+  }
+};
+template <typename TT, int NPL, bool VEC> struct LaneRow;
+template <typename TT, int NPL> struct LaneRow<TT, NPL, true> {        // four neighbouring channels per 128
+  Four<TT> d[NPL / 4];
+  __device__ __forceinline__ void load(const TT* row, int n, int lane) {
 #pragma unroll
     for (int e4 = 0; e4 < NPL / 4; ++e4) {
       const int c = e4 * 128 + 4 * lane;
-      if (c < n) {
-        if constexpr (sizeof(TT) == 2) {
-          const uint2 raw = *reinterpret_cast<const uint2*>(row + c);
-          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-          out[4 * e4] = __bfloat162float(lo.x); out[4 * e4 + 1] = __bfloat162float(lo.y);
-          out[4 * e4 + 2] = __bfloat162float(hi.x); out[4 * e4 + 3] = __bfloat162float(hi.y);
-        } else {
-          const float4 raw = *reinterpret_cast<const float4*>(row + c);
-          out[4 * e4] = raw.x; out[4 * e4 + 1] = raw.y; out[4 * e4 + 2] = raw.z; out[4 * e4 + 3] = raw.w;
-        }
-      } else {
-        out[4 * e4] = out[4 * e4 + 1] = out[4 * e4 + 2] = out[4 * e4 + 3] = 0.f;
-      }
+      if (c < n) d[e4].load(row + c); else d[e4].zero();
     }
-  } else {
+  }
+  __device__ __forceinline__ float get(int e) const { return d[e >> 2].get(e & 3); }
+  static __device__ __forceinline__ int channel(int e, int lane) { return (e >> 2) * 128 + 4 * lane + (e & 3); }
+};
+template <typename TT, int NPL> struct LaneRow<TT, NPL, false> {       // channels 32 apart
+  TT d[NPL];
+  __device__ __forceinline__ void load(const TT* row, int n, int lane) {
 #pragma unroll
     for (int e = 0; e < NPL; ++e) {
       const int c = lane + 32 * e;
-      out[e] = c < n ? co_to_float<TT>(row[c]) : 0.f;
+      d[e] = c < n ? row[c] : co_from_float<TT>(0.f);
     }
   }
-}
-__device__ __forceinline__ int pa_channel(int e, int lane, bool vec) { return vec ? (e >> 2) * 128 + 4 * lane + (e & 3) : lane + 32 * e; }
+  __device__ __forceinline__ float get(int e) const { return co_to_float<TT>(d[e]); }
+  static __device__ __forceinline__ int channel(int e, int lane) { return lane + 32 * e; }
+};
 
-constexpr int PG_WARPS = 16;         // warps of the kernel that shares cached rows among the heads of a key head
-template <typename TT, int HPG, int NPL>
+constexpr int PG_WARPS = 8;          // warps of the kernel that shares cached rows among the heads of a key head
+template <typename TT, int HPG, int NPL, bool VEC>
 __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(AttnArgs A) {
+  using Row = LaneRow<TT, NPL, VEC>;
   extern __shared__ __align__(16) float sm[];
   co_pdl_launch_dependents();
   co_pdl_wait();
@@ -337,7 +354,6 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
   const int g = blockIdx.y, h0 = g * HPG;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int dk = A.dk, dv = A.dv;
-  const bool vec = (dk % 128 == 0) && (dv % 128 == 0);
   float* acc_s = sm;                               // [PG_WARPS][HPG][dv]
   float* ml = acc_s + PG_WARPS * HPG * dv;         // [PG_WARPS][HPG][2]
   float* os = ml + 2 * PG_WARPS * HPG;             // [HPG][dv]
@@ -354,16 +370,21 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
     __syncthreads();
   }
   const int nb = (A.pool > 0 && A.window > 0 && i - A.window + 1 > 0) ? (i - A.window + 1) / A.pool : 0;
-  const int total = nb + (i - lo + 1);
+  // this CTA's share of the row's keys (block means first, then positions): equal runs in multiples of PA_KEYS
+  const int all_keys = nb + (i - lo + 1);
+  const int per_split = ((all_keys + A.splits - 1) / A.splits + PA_KEYS - 1) / PA_KEYS * PA_KEYS;
+  const int first_key = blockIdx.z * per_split;
+  const int total = min(all_keys, first_key + per_split);        // one behind the share's last key
   float qreg[HPG][NPL], acc[HPG][NPL];
 #pragma unroll
   for (int hh = 0; hh < HPG; ++hh) {
-    pa_load_row<TT, NPL>((const TT*)A.q + t * A.ldq + (size_t)(h0 + hh) * dk, dk, vec, lane, qreg[hh]);
+    Row qrow;
+    qrow.load((const TT*)A.q + t * A.ldq + (size_t)(h0 + hh) * dk, dk, lane);
 #pragma unroll
-    for (int e = 0; e < NPL; ++e) acc[hh][e] = 0.f;
+    for (int e = 0; e < NPL; ++e) { qreg[hh][e] = qrow.get(e); acc[hh][e] = 0.f; }
   }
   // the rows of the warp's next keys are requested before the current ones are used (two sets of registers in turn)
-  auto fetch = [&](int n0, float (&kv)[PA_KEYS][NPL], float (&vv)[PA_KEYS][NPL]) {
+  auto fetch = [&](int n0, Row (&kv)[PA_KEYS], Row (&vv)[PA_KEYS]) {
 #pragma unroll
     for (int b = 0; b < PA_KEYS; ++b) {
       const int n = min(n0 + b, total - 1);
@@ -384,8 +405,8 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
         kr = (const TT*)A.k + at * dk;
         vr = (const TT*)A.v + at * dv;
       }
-      pa_load_row<TT, NPL>(kr, dk, vec, lane, kv[b]);
-      pa_load_row<TT, NPL>(vr, dv, vec, lane, vv[b]);
+      kv[b].load(kr, dk, lane);
+      vv[b].load(vr, dv, lane);
     }
   };
   // The scores of an iteration, NS = HPG x PA_KEYS of them, are summed over the lanes so that each ends up in ONE lane
@@ -408,7 +429,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
     for (int rr = 0; rr < LOGN; ++rr) src |= ((idx >> rr) & 1) << (4 - rr);
     return src;
   };
-  auto use = [&](int n0, const float (&kv)[PA_KEYS][NPL], const float (&vv)[PA_KEYS][NPL]) {
+  auto use = [&](int n0, const Row (&kv)[PA_KEYS], const Row (&vv)[PA_KEYS]) {
     float v[NS];
 #pragma unroll
     for (int hh = 0; hh < HPG; ++hh) {
@@ -416,7 +437,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
       for (int b = 0; b < PA_KEYS; ++b) {
         float x = 0.f;
 #pragma unroll
-        for (int e = 0; e < NPL; ++e) x = fmaf(qreg[hh][e], kv[b][e], x);
+        for (int e = 0; e < NPL; ++e) x = fmaf(qreg[hh][e], kv[b].get(e), x);
         v[hh * PA_KEYS + b] = x;
       }
     }
@@ -456,14 +477,14 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
       for (int b = 0; b < PA_KEYS; ++b) {
         const float w = __shfl_sync(0xffffffffu, my_w, source(hh * PA_KEYS + b));
 #pragma unroll
-        for (int e = 0; e < NPL; ++e) acc[hh][e] = fmaf(w, vv[b][e], acc[hh][e]);
+        for (int e = 0; e < NPL; ++e) acc[hh][e] = fmaf(w, vv[b].get(e), acc[hh][e]);
       }
     }
   };
   {
     constexpr int STRIDE = PG_WARPS * PA_KEYS;
-    float ka[PA_KEYS][NPL], va[PA_KEYS][NPL], kb[PA_KEYS][NPL], vb[PA_KEYS][NPL];
-    int n0 = warp * PA_KEYS;
+    Row ka[PA_KEYS], va[PA_KEYS], kb[PA_KEYS], vb[PA_KEYS];
+    int n0 = first_key + warp * PA_KEYS;
     if (n0 < total) fetch(n0, ka, va);
     while (n0 < total) {
       const int n1 = n0 + STRIDE;
@@ -480,7 +501,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
   for (int hh = 0; hh < HPG; ++hh) {
 #pragma unroll
     for (int e = 0; e < NPL; ++e) {
-      const int c = pa_channel(e, lane, vec);
+      const int c = Row::channel(e, lane);
       if (c < dv) acc_s[(warp * HPG + hh) * dv + c] = acc[hh][e];
     }
   }
@@ -489,6 +510,26 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
     ml[2 * (warp * HPG + my_h) + 1] = my_l;
   }
   __syncthreads();
+  if (A.splits > 1) {
+    // the share's sums relative to its own maximum; merge_splits_kernel adds the shares, the sink and the rest
+    float* part = A.scratch + (((size_t)t * A.G + g) * A.splits + blockIdx.z) * (size_t)(HPG * dv + 2 * HPG);
+    for (int e = threadIdx.x; e < HPG * dv + HPG; e += blockDim.x) {
+      const int hh = e < HPG * dv ? e / dv : e - HPG * dv;
+      float top = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < PG_WARPS; ++w) top = fmaxf(top, ml[2 * (w * HPG + hh)]);
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < PG_WARPS; ++w) {
+        const float mw = ml[2 * (w * HPG + hh)];
+        const float fw = mw == -INFINITY ? 0.f : expf(mw - top);
+        o = e < HPG * dv ? fmaf(acc_s[(w * HPG + hh) * dv + (e - hh * dv)], fw, o) : fmaf(ml[2 * (w * HPG + hh) + 1], fw, o);
+      }
+      if (e < HPG * dv) part[e] = o;
+      else { part[HPG * dv + 2 * hh] = top; part[HPG * dv + 2 * hh + 1] = o; }
+    }
+    return;
+  }
   // merge in warp order; the sink joins the denominator once
   for (int e = threadIdx.x; e < HPG * dv; e += blockDim.x) {
     const int hh = e / dv, c = e - hh * dv;
@@ -534,6 +575,62 @@ __global__ void __launch_bounds__(PG_WARPS * 32) pooled_attention_group_kernel(A
   }
 }
 
+// grid (T, H): adds the shares of a row's keys in order, the sink, turns the row back, applies the gate.
+template <typename TT>
+__global__ void merge_splits_kernel(AttnArgs A, int hpg) {
+  extern __shared__ __align__(16) float sm[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  const int h = blockIdx.y, g = h / hpg, hh = h - g * hpg, dv = A.dv;
+  const size_t stride = (size_t)hpg * dv + 2 * hpg;
+  const float* part = A.scratch + ((size_t)t * A.G + g) * A.splits * stride;
+  float* os = sm;              // [dv]
+  float* mls = sm + dv;        // [splits][2]: requested by as many threads at once
+  for (int e = threadIdx.x; e < 2 * A.splits; e += blockDim.x) mls[e] = part[(e >> 1) * stride + hpg * dv + 2 * hh + (e & 1)];
+  __syncthreads();
+  const float sk = A.sinks ? A.sinks[h] : -INFINITY;
+  float top = sk;
+  for (int s2 = 0; s2 < A.splits; ++s2) top = fmaxf(top, mls[2 * s2]);
+  float denom = A.sinks ? expf(sk - top) : 0.f;
+  for (int s2 = 0; s2 < A.splits; ++s2)
+    if (mls[2 * s2] != -INFINITY) denom += mls[2 * s2 + 1] * expf(mls[2 * s2] - top);
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+    float o = 0.f;
+#pragma unroll 8
+    for (int s2 = 0; s2 < A.splits; ++s2) {
+      const float x = part[s2 * stride + hh * dv + c];
+      o = fmaf(x, mls[2 * s2] == -INFINITY ? 0.f : expf(mls[2 * s2] - top), o);
+    }
+    os[c] = o / denom;
+  }
+  __syncthreads();
+  TT* out = (TT*)A.out + t * A.ldo + (size_t)h * dv;
+  const float* gate = A.gates ? A.gates + t * A.ldgate + (size_t)h * dv : nullptr;
+  if (A.freq_v) {
+    const int half = dv / 2;
+    const float p = (float)A.positions[t];
+    for (int c = threadIdx.x; c < half; c += blockDim.x) {
+      float cs, sn;
+      pa_sincos(p, A.freq_v, c, cs, sn);
+      const float a = os[c], b = os[c + half];
+      float x0 = a * cs + b * sn, x1 = b * cs - a * sn;        // turned by -p
+      if (gate) {
+        x0 *= 1.0f / (1.0f + expf(-gate[c]));
+        x1 *= 1.0f / (1.0f + expf(-gate[c + half]));
+      }
+      out[c] = co_from_float<TT>(x0);
+      out[c + half] = co_from_float<TT>(x1);
+    }
+  } else {
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+      float x = os[c];
+      if (gate) x *= 1.0f / (1.0f + expf(-gate[c]));
+      out[c] = co_from_float<TT>(x);
+    }
+  }
+}
+
 template <typename TT>
 static bool launch_grouped(const AttnArgs& A, int T, cudaStream_t stream) {
   const int hpg = A.H / A.G, big = max(A.dk, A.dv);
@@ -542,17 +639,27 @@ static bool launch_grouped(const AttnArgs& A, int T, cudaStream_t stream) {
   if (npl != 4 || (hpg != 1 && hpg != 2 && hpg != 4)) return false;
   const size_t smem = (size_t)(PG_WARPS * hpg * A.dv + 2 * PG_WARPS * hpg + hpg * A.dv + A.table_room) * sizeof(float);
   if (smem > 96 * 1024) return false;
-  // rows whose accesses are vectors must start on vector boundaries
-  if (A.dk % 128 == 0 && A.dv % 128 == 0 && ((A.ldq * sizeof(TT)) % 16 || ((uintptr_t)A.q & 15))) return false;
-  dim3 grid(T, A.G), block(PG_WARPS * 32);
-#define GO(HPG, NPL)                                                                                                        \
-  do {                                                                                                                      \
-    if (smem > 48 * 1024)                                                                                                   \
-      cudaFuncSetAttribute(pooled_attention_group_kernel<TT, HPG, NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    co_launch(pooled_attention_group_kernel<TT, HPG, NPL>, grid, block, smem, stream, A);                                   \
+  // vector accesses: head sizes in multiples of 128 and query rows that start on 16-byte boundaries
+  const bool vec = A.dk % 128 == 0 && A.dv % 128 == 0 && (A.ldq * sizeof(TT)) % 16 == 0 && ((uintptr_t)A.q & 15) == 0;
+  dim3 grid(T, A.G, A.splits), block(PG_WARPS * 32);
+#define GO1(HPG, NPL, VEC)                                                                                                       \
+  do {                                                                                                                           \
+    if (smem > 48 * 1024)                                                                                                        \
+      cudaFuncSetAttribute(pooled_attention_group_kernel<TT, HPG, NPL, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    co_launch(pooled_attention_group_kernel<TT, HPG, NPL, VEC>, grid, block, smem, stream, A);                                   \
+  } while (0)
+#define GO(HPG, NPL)                      \
+  do {                                    \
+    if (vec) GO1(HPG, NPL, true);         \
+    else GO1(HPG, NPL, false);            \
   } while (0)
   if (hpg == 1) GO(1, 4); else if (hpg == 2) GO(2, 4); else GO(4, 4);
 #undef GO
+#undef GO1
+  if (A.splits > 1) {
+    co_count_launch();
+    co_launch(merge_splits_kernel<TT>, dim3(T, A.H), dim3(64), (size_t)(A.dv + 2 * A.splits) * sizeof(float), stream, A, hpg);
+  }
   return true;
 }
 
@@ -599,12 +706,24 @@ CO_EXPORT int coheryn_pooled_means(const void* k_cache, const void* v_cache, voi
   return 0;
 }
 
+// Into how many shares the grouped kernel cuts a row's keys: so that the CTAs fill the SMs about twice, at most eight,
+// one when the step has rows enough by itself or the scratch area (`scratch_floats`) is too small.  A function of the
+// step's row count only.
+CO_EXPORT int coheryn_pooled_attention_splits(int T, int H, int G, int dv, long scratch_floats) {
+  const long ctas = (long)T * G;
+  int splits = (int)(296 / (ctas > 0 ? ctas : 1));
+  if (splits > 8) splits = 8;
+  if (splits < 2) return 1;
+  const long need = (long)T * G * splits * ((long)(H / G) * dv + 2 * (H / G));
+  return scratch_floats >= need ? splits : 1;
+}
+
 CO_EXPORT int coheryn_pooled_attention(const void* q, long ldq, void* out, long ldo, const void* k, const void* v, const void* pk,
                                        const void* pv, int dtype, const int* tables, int table_width, const int* pool_tables,
                                        int pool_table_width, const int* token_req, const int* positions, const float* temps,
                                        const float* sinks, const float* gates, long ldgate, const float* freq_v, int T, int H, int G,
                                        int dk, int dv, int page_size, int window, int pool, int pool_rows, float scale, float cap,
-                                       cudaStream_t stream) {
+                                       float* scratch, long scratch_floats, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H < 1 || G < 1 || H % G) CO_FAIL("pooled_attention: %d heads over %d key heads", H, G);
   if (dk < 1 || dk > 32 * PA_MAX_PER_LANE || dv < 1 || dv > 32 * PA_MAX_PER_LANE)
@@ -612,7 +731,8 @@ CO_EXPORT int coheryn_pooled_attention(const void* q, long ldq, void* out, long 
   if (pool > 0 && (!pk || !pv || !pool_tables)) CO_FAIL("pooled_attention: blocks need their cache");
   AttnArgs A{q, ldq, out, ldo, k, v, pk, pv, tables, table_width, pool_tables, pool_table_width, token_req, positions, temps, sinks,
              gates, ldgate, freq_v, H, G, dk, dv, page_size, window, pool, pool_rows, scale, cap,
-             window > 0 && window / page_size + 2 <= 2048 ? window / page_size + 2 : 0};
+             window > 0 && window / page_size + 2 <= 2048 ? window / page_size + 2 : 0, 1, scratch};
+  A.splits = coheryn_pooled_attention_splits(T, H, G, dv, scratch_floats);
   if (dtype != CO_F32 && dtype != CO_BF16) CO_FAIL("pooled_attention: unknown dtype %d", dtype);
   static const bool grouped = !(getenv("COHERYN_POOLED_GROUPED") && getenv("COHERYN_POOLED_GROUPED")[0] == '0');
   if (grouped && (dtype == CO_F32 ? launch_grouped<float>(A, T, stream) : launch_grouped<__nv_bfloat16>(A, T, stream))) {

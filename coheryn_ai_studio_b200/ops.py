@@ -1751,10 +1751,13 @@ def pooled_attention(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, pk_ca
             c_float(scale), c_float(softcap or 0.0), _stream()))
         return
     lib = pooled()
+    # few rows (decoding): the keys of a row are shared out over several CTAs, whose parts meet in a scratch area
+    floats = T * heads * (dv + 2) * 8 if T * kv_heads < 148 else 0
+    scratch = torch.empty(floats, dtype=torch.float32, device=q.device) if floats else None
     _check(lib, lib.coheryn_pooled_attention(
         _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(pk_cache),
         _ptr(pv_cache), c_int(_code(q)), _ptr(tables), c_int(tables.shape[1]), _ptr(ptables),
         c_int(ptables.shape[1] if ptables is not None else 0), _ptr(step.token_req), _ptr(step.positions), _ptr(temps), _ptr(sinks),
         _ptr(gates), c_long(gates.stride(0) if gates is not None else 0), _ptr(freq_v), c_int(T), c_int(heads), c_int(kv_heads),
         c_int(dk), c_int(dv), c_int(page_size), c_int(window or 0), c_int(pool or 0),
-        c_int(pk_cache.shape[2] if pool else 0), c_float(scale), c_float(softcap or 0.0), _stream()))
+        c_int(pk_cache.shape[2] if pool else 0), c_float(scale), c_float(softcap or 0.0), _ptr(scratch), c_long(floats), _stream()))
