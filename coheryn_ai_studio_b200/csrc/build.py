@@ -269,7 +269,10 @@ def pooled_attention_tc_library(dk: int, dv: int) -> ctypes.CDLL:
     if dk % 16 or dv % 16 or not 16 <= dk <= 256 or not 16 <= dv <= 128:
         raise BuildError(f"the tensor-core window attention takes key channels 16..256 and value channels 16..128 in steps "
                          f"of 16, not ({dk}, {dv})")
-    return load_library(f"pooled_tc_{dk}_{dv}", ["attention_pooled_tc.cu", "runtime.cu"], {"CO_PW_DK": dk, "CO_PW_DV": dv})
+    defines = {"CO_PW_DK": dk, "CO_PW_DV": dv}
+    if os.environ.get("COHERYN_POOLED_BN"):       # a measuring switch: keys per tile (32 or 64)
+        defines["CO_PW_BN"] = int(os.environ["COHERYN_POOLED_BN"])
+    return load_library(f"pooled_tc_{dk}_{dv}", ["attention_pooled_tc.cu", "runtime.cu"], defines)
 
 
 def routed_library() -> ctypes.CDLL:
