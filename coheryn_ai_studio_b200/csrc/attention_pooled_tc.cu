@@ -7,8 +7,8 @@
 //     rest), then the positions from the first one its FIRST row sees, counted in absolute multiples of BN so that a row's
 //     sums do not depend on where its portion was cut; rows and channels of a tile arrive by cp.async through the two
 //     block tables, two stages deep;
-//   * scores S = Q K^T in float32, times scale * temp[head], capped by cap * tanh(S / cap), masked; online softmax in
-//     float32; a weight enters the product with the values as the sum of two bfloat16 numbers (high + low part), so that it
+//   * scores S = Q K^T in float32, times scale * temp[head], capped by cap * tanh(S / cap) (computed as
+//     cap - 2 cap / (exp(2 S / cap) + 1), in units of log 2), masked; online softmax in float32; a weight enters the product with the values as the sum of two bfloat16 numbers (high + low part), so that it
 //     carries sixteen bits of mantissa; the sink joins the denominator at the end;
 //   * epilogue: the row divided by its denominator, turned back by minus its position over all value channels (the pair
 //     (c, c + dv/2) sits in one thread), multiplied by sigmoid(gate), written as bfloat16.
@@ -80,6 +80,19 @@ __device__ __forceinline__ void split_pack(float x, float y, unsigned& hi, unsig
   const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
   hi = pack_bf16(__bfloat162float(xh), __bfloat162float(yh));
   lo = pack_bf16(x - __bfloat162float(xh), y - __bfloat162float(yh));
+}
+
+// 2^x and 1/x by the special-function unit (relative error about 2^-22): the scores live in units of log 2 from the cap
+// on, so a weight is one subtraction and one of these.
+__device__ __forceinline__ float tc_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float tc_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ void tc_sincos(float p, const float* freq, int i, float& c, float& s) {
@@ -228,16 +241,13 @@ __global__ void __launch_bounds__(WARPS * 32) pooled_attention_tc_kernel(TcArgs 
         else inner = first + BN - 1 <= wa && (A.window <= 0 || first >= wb - A.window + 1);
       }
       float ta = -INFINITY, tb = -INFINITY;
-      const float two_inv_cap = 2.0f * inv_cap * LOG2E;
+      // in units of log 2: x2 = score * scale * factor * log2(e), capped as C - 2 C / (2^(2 x2 / C) + 1) with C = cap * log2(e)
+      const float cap2 = A.cap * LOG2E, to_exp = mult * 2.0f * inv_cap * LOG2E, to_log2 = mult * LOG2E;
 #pragma unroll
       for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float x = s[n][e] * mult;
-          // cap tanh(x / cap) = cap (1 - 2 / (exp(2 x / cap) + 1)): absolute error a few 1e-7 of the cap
-          if (A.cap > 0.f) x = A.cap - __fdividef(2.0f * A.cap, exp2f(x * two_inv_cap) + 1.0f);
-          s[n][e] = x;
-        }
+        for (int e = 0; e < 4; ++e)
+          s[n][e] = A.cap > 0.f ? fmaf(-2.0f * cap2, tc_rcp(tc_ex2(s[n][e] * to_exp) + 1.0f), cap2) : s[n][e] * to_log2;
       }
       if (!inner) {
 #pragma unroll
@@ -262,20 +272,22 @@ __global__ void __launch_bounds__(WARPS * 32) pooled_attention_tc_kernel(TcArgs 
       tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)); tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
       const float na = fmaxf(ma, ta), nb_ = fmaxf(mb, tb);
       const float base_a = na == -INFINITY ? 0.f : na, base_b = nb_ == -INFINITY ? 0.f : nb_;
-      const float fa = exp2f((ma - base_a) * LOG2E), fb = exp2f((mb - base_b) * LOG2E);     // exp(-inf) = 0 while nothing was seen
+      const float fa = tc_ex2(ma - base_a), fb = tc_ex2(mb - base_b);     // 2^(-inf) = 0 while nothing was seen
       ma = na; mb = nb_;
       float sa = 0.f, sb = 0.f;
 #pragma unroll
       for (int n = 0; n < BN / 8; ++n) {
-        s[n][0] = exp2f((s[n][0] - base_a) * LOG2E); s[n][1] = exp2f((s[n][1] - base_a) * LOG2E);
-        s[n][2] = exp2f((s[n][2] - base_b) * LOG2E); s[n][3] = exp2f((s[n][3] - base_b) * LOG2E);
+        s[n][0] = tc_ex2(s[n][0] - base_a); s[n][1] = tc_ex2(s[n][1] - base_a);
+        s[n][2] = tc_ex2(s[n][2] - base_b); s[n][3] = tc_ex2(s[n][3] - base_b);
         sa += s[n][0] + s[n][1];
         sb += s[n][2] + s[n][3];
       }
       la = la * fa + sa;
       lb = lb * fb + sb;
+      if (__any_sync(0xffffffffu, fa != 1.f || fb != 1.f)) {        // most tiles raise no row's maximum
 #pragma unroll
-      for (int n = 0; n < DV / 8; ++n) { o[n][0] *= fa; o[n][1] *= fa; o[n][2] *= fb; o[n][3] *= fb; }
+        for (int n = 0; n < DV / 8; ++n) { o[n][0] *= fa; o[n][1] *= fa; o[n][2] *= fb; o[n][3] *= fb; }
+      }
       // O += P V, the weights as high + low parts
 #pragma unroll
       for (int kk = 0; kk < BN / 16; ++kk) {
@@ -304,11 +316,11 @@ __global__ void __launch_bounds__(WARPS * 32) pooled_attention_tc_kernel(TcArgs 
   lb += __shfl_xor_sync(0xffffffffu, lb, 1); lb += __shfl_xor_sync(0xffffffffu, lb, 2);
   float scale_a, scale_b;
   if (A.sinks) {
-    const float sk = A.sinks[h];
+    const float sk = A.sinks[h] * LOG2E;          // the maxima are in units of log 2
     const float top_a = fmaxf(ma, sk), top_b = fmaxf(mb, sk);
-    const float ka = exp2f((ma - top_a) * LOG2E), kb = exp2f((mb - top_b) * LOG2E);
-    scale_a = ka / (la * ka + exp2f((sk - top_a) * LOG2E));
-    scale_b = kb / (lb * kb + exp2f((sk - top_b) * LOG2E));
+    const float ka = exp2f(ma - top_a), kb = exp2f(mb - top_b);
+    scale_a = ka / (la * ka + exp2f(sk - top_a));
+    scale_b = kb / (lb * kb + exp2f(sk - top_b));
   } else {
     scale_a = 1.0f / la;
     scale_b = 1.0f / lb;
